@@ -1,0 +1,194 @@
+/* b200mlp: C ABI of the B200 (sm_100a) implementation of the MLP training step
+ * benchmarked by jspark1105/tbb_test (mlp_omp.cc / mlp_tbb.cc).
+ *
+ * The reference has no FFI layer: its hot path is reached at source level from
+ * main() (mlp_omp.cc:375-750) through the globals of mlp_bench_common.h:53-55.
+ * Each entry point below replaces one phase of that main; the citation names the
+ * reference code it stands in for.  One handle drives one GPU (the reference's
+ * "socket"); a data-parallel job creates one handle per GPU, in one process or in
+ * one process per GPU, all with the same configuration except `rank`/`device`.
+ *
+ * Conventions: plain pointers and sizes only; host matrices are row-major with a
+ * caller-given leading dimension in ELEMENTS (the reference's Matrix has
+ * ld = ncols + 16, Matrix.h:148); every function returns a b2_status (0 = ok,
+ * negative = error, b2_last_error() gives the text) and never exits or throws
+ * (the reference asserts or calls exit(-1), mlp_omp.cc:368).  There is no CPU
+ * fallback: without a usable CUDA device b2_create fails.
+ */
+#ifndef B200MLP_H
+#define B200MLP_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct b2_handle b2_handle;
+
+typedef enum {
+  B2_OK = 0,
+  B2_ERR_INVALID = -1,     /* bad argument or shape */
+  B2_ERR_CUDA = -2,        /* a CUDA runtime/driver call failed */
+  B2_ERR_NCCL = -3,        /* NCCL missing or a collective failed */
+  B2_ERR_UNSUPPORTED = -4, /* valid request this build cannot serve */
+  B2_ERR_TIMEOUT = -5,     /* a bounded device-side wait gave up */
+  B2_ERR_STATE = -6        /* call made in the wrong state */
+} b2_status;
+
+/* What the step computes. */
+typedef enum {
+  B2_MODE_REF = 0,     /* the C++ reference as written: no ReLU, dZ[L-1] = A[L]
+                          (mlp_omp.cc:565,655), no 1/B scaling */
+  B2_MODE_BASELINE = 1 /* ReLU between layers, dZ[L-1] = (A[L]-T)/B_global
+                          (c2_bench/mlp_caffe2.py:208-235) */
+} b2_mode;
+
+/* Arithmetic of the three GEMMs; accumulation is fp32 and the master weights and
+ * the SGD update are fp32 in every case. */
+typedef enum {
+  B2_PREC_FP32 = 0, /* fp32 operands, CUDA-core FMA (parity mode) */
+  B2_PREC_TF32 = 1, /* fp32 storage, tcgen05 kind::tf32 */
+  B2_PREC_BF16 = 2  /* bf16 operands (activations, gradients, a bf16 weight copy),
+                       tcgen05 kind::f16 */
+} b2_precision;
+
+typedef enum { B2_DTYPE_F32 = 0, B2_DTYPE_BF16 = 1 } b2_dtype;
+
+/* Replaces the compile-time model of mlp_bench_common.h:26-38 and the argv of
+ * mlp_omp.cc:376-386. Fill with b2_config_default() first. */
+typedef struct {
+  int nlayers;              /* number of fully-connected layers L */
+  const int* nfeatures;     /* L+1 widths F_0..F_L (mlp_bench_common.h:26) */
+  int batch;                /* GLOBAL batch, split over ranks like
+                               get_partition(batch, rank, 1, 0) (Partition.cc:34-51) */
+  int rank;                 /* this handle's shard, 0 <= rank < world_size  (socket id) */
+  int world_size;           /* number of GPUs in the job                   (nsockets) */
+  int device;               /* CUDA device ordinal */
+  int mode;                 /* b2_mode */
+  int precision;            /* b2_precision */
+  int grad_bf16;            /* 1: weight gradients are produced, summed and read in bf16
+                               (BF16 precision only) */
+  int allreduce;            /* 0 = the reference's NO_ALL_REDUCE build (mlp_omp.cc:21) */
+  int overlap;              /* 1 = allreduce/update on a side stream, overlapped with the
+                               remaining backward GEMMs (OVERLAP_ALL_REDUCE, mlp_omp.cc:23) */
+  int input_grad;           /* 1 = also compute dA[0] like the reference (mlp_omp.cc:656) */
+  int collect_timing;       /* 1 = per-phase CUDA-event timing (sum_times, mlp_bench_common.h:35) */
+  int use_graph;            /* 1 = replay each step as one CUDA graph */
+  int force_simt;           /* 1 = never use the tensor-core kernels (debugging aid) */
+  float lr;                 /* SGD step (the reference hard-codes 1e-10, mlp_omp.cc:609) */
+  const void* nccl_unique_id; /* B2_NCCL_ID_BYTES bytes from b2_nccl_unique_id(), shared by all
+                                 ranks; NULL when world_size == 1 */
+} b2_config;
+
+#define B2_NCCL_ID_BYTES 128
+
+/* Phases of the step, in the order of the reference's Breakdown enum
+ * (mlp_bench_common.h:12-20). */
+enum { B2_T_FWD = 0, B2_T_WGT_GRAD = 1, B2_T_BWD = 2, B2_T_WGT_UPDATE = 3,
+       B2_T_ALLREDUCE = 4, B2_T_NUM = 5 };
+
+/* Defaults: mode BASELINE, precision FP32, world 1, allreduce/overlap/input_grad on. */
+int b2_config_default(b2_config* cfg);
+
+/* Library version string and the CUDA architecture it was built for. */
+const char* b2_version(void);
+
+/* Root rank: create the id every rank passes in b2_config.nccl_unique_id. */
+int b2_nccl_unique_id(void* out_bytes);
+
+/* Allocation phase of main (mlp_omp.cc:390-409): device buffers for weights,
+ * gradients and activations of this rank's batch shard, streams, events and the
+ * communicator. */
+int b2_create(const b2_config* cfg, b2_handle** out);
+int b2_destroy(b2_handle* h);
+
+/* Text of the last error recorded on the handle (or on the calling thread when
+ * h is NULL, e.g. after a failed b2_create). */
+const char* b2_last_error(const b2_handle* h);
+
+/* Rows [begin,end) of the global batch this handle owns (Partition.cc:34-51). */
+int b2_batch_range(const b2_handle* h, int* begin, int* end);
+
+/* init_matrices (mlp_bench_common.cc:16-33): weights[l] replica rows, F_{l+1} x F_l. */
+int b2_upload_weights(b2_handle* h, int layer, const float* host, size_t ld);
+int b2_download_weights(b2_handle* h, int layer, float* host, size_t ld);
+/* activations[0] (mlp_bench_common.cc:18) and the +-1 targets of BASELINE mode.
+ * `host` is the GLOBAL batch x F matrix; the handle copies its own rows. */
+int b2_upload_input(b2_handle* h, const float* host, size_t ld);
+int b2_upload_target(b2_handle* h, const float* host, size_t ld);
+
+/* Parity taps. `host` is the GLOBAL batch x F matrix; only this handle's rows are
+ * written. Activation l in [0,L]; dz l in [0,L-1] is the gradient w.r.t. layer l's
+ * output (what the reference leaves in activations[l+1], mlp_omp.cc:655-671). */
+int b2_download_activation(b2_handle* h, int layer, float* host, size_t ld);
+int b2_download_dz(b2_handle* h, int layer, float* host, size_t ld);
+int b2_download_input_grad(b2_handle* h, float* host, size_t ld);
+/* weight_grads[l] (mlp_omp.cc:579): this rank's gradient, after the allreduce if
+ * one has run. */
+int b2_download_weight_grad(b2_handle* h, int layer, float* host, size_t ld);
+int b2_upload_weight_grad(b2_handle* h, int layer, const float* host, size_t ld);
+
+int b2_set_lr(b2_handle* h, float lr);
+
+/* The loop body of mlp_omp.cc:435-737, `iters` times: forward GEMMs, output
+ * gradient, then per layer (last to first) weight-gradient GEMM, gradient
+ * allreduce + SGD on the side stream, input-gradient GEMM. Returns after both
+ * streams have drained. */
+int b2_step(b2_handle* h, int iters);
+
+/* One step fed from host memory: uploads this rank's rows of `x` (and `t`),
+ * runs b2_step(h, 1) and returns this rank's share of the loss
+ * (0.5*sum((Y-T)^2)/B_global, or 0.5*sum(Y^2) in REF mode). Pinned host memory
+ * (b2_host_alloc) makes the copies asynchronous. */
+int b2_train_step_host(b2_handle* h, const float* x, size_t ldx, const float* t, size_t ldt,
+                       double* loss);
+/* Loss of the most recent step (this rank's share). */
+int b2_loss(b2_handle* h, double* loss);
+
+int b2_host_alloc(void** ptr, size_t bytes); /* pinned host memory */
+int b2_host_free(void* ptr);
+
+/* The three cblas_sgemm call sites (mlp_omp.cc:474,566,657) with cblas argument
+ * meaning, row-major, on HOST matrices (copied in and out): C = op(A)*op(B) in the
+ * given b2_precision, optional fused ReLU (epilogue 1) or mask by aux>0
+ * (epilogue 2, aux is m x n with leading dimension ldaux). */
+int b2_sgemm_host(b2_handle* h, int precision, int transa, int transb, int m, int n, int k,
+                  const float* a, size_t lda, const float* b, size_t ldb, float* c, size_t ldc,
+                  int epilogue, const float* aux, size_t ldaux);
+/* Same on fp32 DEVICE pointers of this handle's GPU, alpha/beta like cblas
+ * (FP32 precision: any alpha/beta; TF32: beta must be 0). Asynchronous on the
+ * handle's main stream; b2_sync() waits. */
+int b2_sgemm(b2_handle* h, int precision, int transa, int transb, int m, int n, int k, float alpha,
+             const float* a, size_t lda, const float* b, size_t ldb, float beta, float* c,
+             size_t ldc);
+int b2_sync(b2_handle* h);
+
+/* update_weight (mlp_omp.cc:297-323) on layer `l`: sum weight_grads[l] over all
+ * ranks, then w = fma(-lr, sum, w). The reference's known-answer test
+ * (mlp_omp.cc:325-373) runs through this call. */
+int b2_allreduce_sgd(b2_handle* h, int layer);
+
+/* Gradient-allreduce sweep: sums `count` elements of `dtype` filled with
+ * U(-1,1) from seed = rank across all ranks, `iters` timed repetitions after
+ * `warmup`; *ms_per_iter is the device time of one allreduce on this rank and
+ * checksum (optional) the sum of the first min(count,4096) result elements. */
+int b2_allreduce_bench(b2_handle* h, size_t count, int dtype, int warmup, int iters,
+                       double* ms_per_iter, double* checksum);
+
+/* Device times in milliseconds accumulated since the last reset:
+ * phase_ms[l * B2_T_NUM + phase] per layer (needs collect_timing), and
+ * *step_ms / *steps for whole steps (always collected). Feeds report_timing
+ * (mlp_bench_common.cc:38-150). Pointers may be NULL. */
+int b2_get_timing(b2_handle* h, double* phase_ms, double* step_ms, long long* steps);
+int b2_reset_timing(b2_handle* h);
+
+/* Number of kernels of this library launched on the handle since creation, and
+ * how many of them were tensor-core (tcgen05) GEMMs. */
+int b2_launch_counts(const b2_handle* h, long long* total, long long* tensor_core);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200MLP_H */
