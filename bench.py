@@ -1,0 +1,361 @@
+#!/usr/bin/env python
+"""Benchmark of the MLP training step (samples/s) on 1..8 B200s of one box.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload c4|c1|c3] [--precision bf16|tf32|fp32]
+
+One process per GPU (torchrun sets RANK / LOCAL_RANK / WORLD_SIZE); rank 0 prints
+ONE JSON line.  A step is one pass of the hot path (forward, output gradient,
+weight-gradient + input-gradient GEMMs per layer, gradient allreduce, SGD) over
+one global batch of seeded synthetic data.  The default workload is the widest
+configuration that fits one GPU: 8 layers of 4096x4096, global batch 8192,
+bf16 tensor-core operands with fp32 accumulation and fp32 master weights; with
+N GPUs the global batch is split evenly (strong scaling) and each layer's 64 MiB
+fp32 gradient is summed with NCCL on a side stream.
+
+value     global batch * K / device time of K steps (CUDA events on the launching
+          stream inside the library; max over ranks), inputs resident in HBM
+e2e       same metric through b2_train_step_host: every step copies that step's
+          inputs and targets from pinned host memory and reads the loss back
+roofline  the GEMMs: 2mnk flops of all GEMM launches / their summed event time,
+          against the measured cuBLAS bf16 peak of MEASURED_PEAKS.json
+cpu_baseline / --impl reference
+          the reference's own mlp_omp (oracle/_ref, built from the unmodified
+          sources with only the workload literals replaced) timed on the host cores
+"""
+import argparse
+import json
+import os
+import re
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (layer widths, global batch, weight init, description)
+    "c1": ([1024] * 6, 1024, ("uniform", 1.0 / 32), "5 x 1024^2, batch 1024"),
+    "c3": ([512] * 21, 2048, ("uniform", 512 ** -0.5), "20 x 512^2, batch 2048"),
+    "c4": ([4096] * 9, 8192, ("uniform", 1.0 / 64), "8 x 4096^2, batch 8192"),
+}
+
+
+def env_int(name, default):
+    try:
+        return int(os.environ.get(name, default))
+    except ValueError:
+        return default
+
+
+def host_cores():
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def has_avx512():
+    try:
+        with open("/proc/cpuinfo") as f:
+            return "avx512f" in f.read()
+    except Exception:
+        return False
+
+
+def pick_sockets_threads(cores):
+    """(sockets, threads/socket) for mlp_omp: the reference's self-check only passes for
+    1, 2 or 8 sockets with several threads each, and its thread table stops at 28
+    (mlp_bench_common.h:40-48). Choose the pair with the most GEMM threads."""
+    comm = lambda t: 0 if t < 5 else 1 if t < 10 else 2 if t < 20 else 4
+    best = (1, max(1, min(cores, 28)))
+    best_score = best[1] - comm(best[1])
+    for s in (2, 8):
+        t = min(cores // s, 28)
+        if t >= 5:
+            score = s * (t - comm(t))
+            if score > best_score:
+                best, best_score = (s, t), score
+    return best
+
+
+def run_reference_cpu(workload, batch):
+    """Times oracle/_ref/mlp_omp_<workload> on the host cores. Returns a dict or None."""
+    exe = os.path.join(ROOT, "oracle", "_ref", f"mlp_omp_{workload}")
+    if not os.path.exists(exe) or not has_avx512():
+        return None
+    cores = host_cores()
+    s, t = pick_sockets_threads(cores)
+    env = dict(os.environ, OMP_PROC_BIND="close", OMP_PLACES="cores", OPENBLAS_NUM_THREADS="1",
+               OMP_NUM_THREADS=str(s * t))
+    t0 = time.time()
+    try:
+        r = subprocess.run([exe, str(s), str(t)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                           text=True, timeout=900)
+    except subprocess.TimeoutExpired:
+        return None
+    m = re.search(r"wall clock time ([0-9.eE+-]+) ms/iter", r.stdout)
+    if r.returncode != 0 or not m:
+        return None
+    ms = float(m.group(1))
+    it = {"c1": (2, 8), "c3": (2, 8), "c4": (1, 2)}[workload]
+    return {"value": batch / (ms / 1e3), "ms_per_step": ms, "cores": s * t, "sockets": s, "kind": "reference",
+            "unit": "samples/s", "wall_s": round(time.time() - t0, 1),
+            "sample": f"unmodified mlp_omp built with this workload's widths/batch, {s} socket(s) x {t} threads, "
+                      f"OpenBLAS sgemm, {it[0]} warm-up + {it[1]} timed steps of the full workload"}
+
+
+def run_port_cpu(nf, batch, steps=1):
+    """Fallback CPU baseline: the oracle port with OpenBLAS on all cores (bounded sample)."""
+    from oracle import oracle as O
+    import numpy as np
+    cores = host_cores()
+    O.use_openblas(threads=cores)
+    rows = min(batch, 1024)  # bounded sample: a 1024-row slice of the batch
+    orc = O.Oracle(nf, rows, mode=O.MODE_REF, lr=1e-10)
+    rng = np.random.default_rng(0)
+    for l in range(len(nf) - 1):
+        orc.set_weights(l, rng.uniform(-0.01, 0.01, (nf[l + 1], nf[l])).astype(np.float32))
+    orc.set_input(rng.standard_normal((rows, nf[0]), dtype=np.float32))
+    orc.step(1)
+    t0 = time.time()
+    orc.step(steps)
+    dt = (time.time() - t0) / steps
+    O.use_builtin_gemm()
+    return {"value": rows / dt, "ms_per_step": dt * 1e3, "cores": cores, "kind": "port", "unit": "samples/s",
+            "sample": f"oracle port (OpenBLAS, {cores} threads) on a {rows}-row slice of the batch, {steps} step(s)"}
+
+
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.p = None
+        self.idx = gpu_index
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                       "-lms", "100", "-i", str(gpu_index)], stdout=subprocess.PIPE,
+                                      stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.p = None
+
+    def stop(self):
+        if not self.p:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.p.terminate()
+        try:
+            out, _ = self.p.communicate(timeout=5)
+        except Exception:
+            self.p.kill()
+            out = ""
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        hi = [v for v in sm if v >= 0.5 * max(sm)]  # samples under load
+        return {"sm_mhz": statistics.median(hi), "sm_max_mhz": max(smax), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return p, "measured"
+    except Exception:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS))
+    ap.add_argument("--precision", default="bf16", choices=["bf16", "tf32", "fp32"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-graph", action="store_true")
+    args = ap.parse_args()
+
+    rank, world = env_int("RANK", 0), env_int("WORLD_SIZE", 1)
+    local_rank = env_int("LOCAL_RANK", 0)
+    nf, batch, winit, desc = WORKLOADS[args.workload]
+    warmup = max(args.warmup, 3)
+    L = len(nf) - 1
+    cfg_common = {"workload": f"{args.workload}: MLP {desc}, ReLU, +-1 targets, SGD lr 0.01; "
+                              f"global batch split over {world} GPU(s)",
+                  "global_batch": batch, "layers": L, "width": nf[0],
+                  "parallelism": f"dp{world}", "l2": "working set per step exceeds the 126 MB L2 "
+                  "(weights + activations of all layers are re-read every step)"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return 0
+        ref = run_reference_cpu(args.workload, batch)
+        if ref is None:
+            ref = run_port_cpu(nf, batch)
+        line = {"impl": "reference", "metric": "mlp_train_samples_per_sec", "value": ref["value"],
+                "unit": "samples/s", "n_gpus": 0, "steps": args.steps, "warmup": warmup,
+                "ms_per_step": ref["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg_common,
+                "cpu_baseline": {k: ref[k] for k in ("value", "unit", "cores", "kind", "sample")},
+                "e2e": {"value": ref["value"], "unit": "samples/s", "h2d_bytes_per_step": 0,
+                        "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
+        print(json.dumps(line))
+        return 0
+
+    import numpy as np
+    import torch
+    from tbb_test_b200 import _capi as K
+    from tbb_test_b200.mlp import MLP, nccl_unique_id, pinned_array
+
+    torch.cuda.set_device(local_rank)
+    dist = None
+    nccl_id = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        box = [nccl_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        nccl_id = box[0]
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v):
+        if dist is None:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum_over_ranks(v):
+        if dist is None:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
+    prec = {"bf16": K.PREC_BF16, "tf32": K.PREC_TF32, "fp32": K.PREC_FP32}[args.precision]
+    dev = MLP(nf, batch, rank=rank, world_size=world, device=local_rank, mode=K.MODE_BASELINE, precision=prec,
+              lr=0.01, nccl_id=nccl_id, collect_timing=True)
+    b0, b1 = dev.rows
+
+    # seeded synthetic data (weights seed 0, inputs seed 1, targets seed 2); every rank
+    # draws the same weights and only its own rows of the batch
+    rng_w = np.random.default_rng(0)
+    for l in range(L):
+        a = winit[1]
+        dev.upload_weights(l, rng_w.uniform(-a, a, (nf[l + 1], nf[l])).astype(np.float32))
+    x_host = pinned_array((batch, nf[0]))
+    t_host = pinned_array((batch, nf[-1]))
+    rng_x = np.random.default_rng([1, rank])
+    rng_t = np.random.default_rng([2, rank])
+    x_host[b0:b1] = rng_x.standard_normal((b1 - b0, nf[0]), dtype=np.float32)
+    t_host[b0:b1] = np.where(rng_t.random((b1 - b0, nf[-1])) < 0.5, -1.0, 1.0).astype(np.float32)
+    dev.upload_input(x_host)
+    dev.upload_target(t_host)
+
+    # ---- device-resident timing -------------------------------------------------
+    sampler = ClockSampler(local_rank) if rank == 0 else None  # started early: nvidia-smi needs a moment
+    dev.step(warmup)
+    dev.reset_timing()
+    l0, tc0 = dev.launch_counts()
+    barrier()
+    dev.step(args.steps)
+    barrier()
+    clocks = sampler.stop() if sampler else None  # idle samples are dropped, see ClockSampler.stop
+    phase_ms, step_ms, nsteps = dev.timing()
+    l1, tc1 = dev.launch_counts()
+    ms_per_step = max_over_ranks(step_ms / max(nsteps, 1))
+    value = batch / (ms_per_step / 1e3)
+    launches = int(sum_over_ranks(l1 - l0))
+    loss = sum_over_ranks(dev.loss())
+
+    # roofline of the GEMMs on this rank (flops of the launches / their event time)
+    bl = b1 - b0
+    gemm_flops = sum(3 * 2.0 * bl * nf[l] * nf[l + 1] for l in range(L)) * nsteps
+    gemm_ms = float(phase_ms[:, [K.T_FWD, K.T_WGT_GRAD, K.T_BWD]].sum())
+    peaks, peak_kind = measured_peaks()
+    achieved_tf = gemm_flops / (gemm_ms / 1e3) / 1e12 if gemm_ms > 0 else 0.0
+    peak_tf = peaks.get("bf16_tflops_sustained", 1400.0)
+    per_phase = {n: float(phase_ms[:, i].sum() / max(nsteps, 1)) for n, i in
+                 (("fwd_ms", K.T_FWD), ("wgrad_ms", K.T_WGT_GRAD), ("dgrad_ms", K.T_BWD),
+                  ("sgd_ms", K.T_WGT_UPDATE), ("allreduce_ms", K.T_ALLREDUCE))}
+    n_params = sum(nf[l] * nf[l + 1] for l in range(L))
+    sgd_bytes = n_params * (14 if args.precision == "bf16" else 12)
+    sgd_gbs = sgd_bytes / (per_phase["sgd_ms"] / 1e3) / 1e9 if per_phase["sgd_ms"] > 0 else 0.0
+    roofline = {"bound": "tensor", "kernel": "gemm_tc_kernel (fwd + wgrad + dgrad launches)",
+                "achieved": achieved_tf, "peak": peak_tf, "unit": "TFLOP/s",
+                "frac": achieved_tf / peak_tf if peak_tf else None, "traffic": None,
+                "peak_source": f"{peak_kind}: cuBLAS bf16 sustained ({peaks.get('bf16_tflops')} burst)",
+                "per_step_ms": per_phase,
+                "sgd": {"bound": "hbm", "achieved": sgd_gbs, "peak": peaks.get("hbm_gbs"), "unit": "GB/s",
+                        "frac": sgd_gbs / peaks["hbm_gbs"] if peaks.get("hbm_gbs") else None,
+                        "note": "runs on the side stream concurrently with GEMMs"}}
+    if world > 1 and per_phase["allreduce_ms"] > 0:
+        ar_bytes = n_params * 4
+        roofline["allreduce"] = {"busbw_gbs": ar_bytes * 2 * (world - 1) / world / (per_phase["allreduce_ms"] / 1e3) / 1e9,
+                                 "note": "per-layer ncclAllReduce timed on the side stream while GEMMs run"}
+
+    # ---- end to end through the host-facing call --------------------------------
+    e2e = None
+    if not args.no_e2e:
+        xp = x_host.ctypes.data_as(K._fp)
+        tp = t_host.ctypes.data_as(K._fp)
+        for _ in range(3):
+            dev.train_step_host(xp, nf[0], tp, nf[-1])
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            dev.train_step_host(xp, nf[0], tp, nf[-1])
+        torch.cuda.synchronize()
+        dt = max_over_ranks(time.perf_counter() - t0)
+        e2e = {"value": batch * args.steps / dt, "unit": "samples/s",
+               "h2d_bytes_per_step": batch * (nf[0] + nf[-1]) * 4, "d2h_bytes_per_step": 8 * world,
+               "ms_per_step": dt / args.steps * 1e3}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu = run_reference_cpu(args.workload, batch) or run_port_cpu(nf, batch)
+        cpu = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+
+    dev.close()
+    if rank == 0:
+        line = {"metric": "mlp_train_samples_per_sec", "value": value, "unit": "samples/s", "n_gpus": world,
+                "steps": args.steps, "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": args.precision, "data": "synthetic",
+                "config": cfg_common, "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
+                "gpu_launches": launches, "clocks": clocks, "loss": loss,
+                "gemm_tflops_per_gpu": achieved_tf}
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

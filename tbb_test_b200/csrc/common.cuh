@@ -1,0 +1,64 @@
+// Shared declarations of the b200mlp CUDA sources (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b2 {
+
+enum Epilogue : int {
+  EPI_NONE = 0,  // C = alpha * acc (+ beta * C)
+  EPI_RELU = 1,  // C = max(acc, 0)                    forward of a hidden layer
+  EPI_MASK = 2   // C = aux > 0 ? acc : 0              input gradient through a ReLU
+};
+
+enum ElemType : int { T_F32 = 0, T_BF16 = 1 };
+
+// One GEMM, C[M x N] = op(A) * op(B), described by element strides so that the
+// three call forms of the training step share every kernel:
+//   forward  (NoTrans x Trans)   A(m,k) = A[m*lda + k]   B(k,n) = B[n*ldb + k]
+//   wgrad    (Trans   x NoTrans) A(m,k) = A[k*lda + m]   B(k,n) = B[k*ldb + n]
+//   dgrad    (NoTrans x NoTrans) A(m,k) = A[m*lda + k]   B(k,n) = B[k*ldb + n]
+struct GemmDesc {
+  int M, N, K;
+  const void* A;
+  long long sAm, sAk;
+  const void* B;
+  long long sBk, sBn;
+  void* C;
+  long long ldc;
+  const void* aux;  // EPI_MASK only, same element type as A/B operands
+  long long ldaux;
+  float alpha, beta;
+  int epilogue;
+  int in_type;   // ElemType of A, B and aux
+  int out_type;  // ElemType of C
+};
+
+// CUDA-core GEMM for any shape, stride and alignment (fp32 accumulate).
+cudaError_t gemm_simt_launch(const GemmDesc& g, cudaStream_t stream);
+
+// Tensor-core (tcgen05 + TMA + TMEM) GEMM. in_type T_BF16 -> kind::f16 (bf16),
+// in_type T_F32 -> kind::tf32. Returns cudaErrorNotSupported when the shape or
+// alignment cannot be served (caller falls back to gemm_simt_launch).
+// `status` is a device word the kernel sets non-zero if a bounded wait gave up.
+struct TcPlan;  // opaque: tensor maps + tile choice for one GEMM site
+TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t errlen);
+void gemm_tc_plan_destroy(TcPlan* p);
+cudaError_t gemm_tc_launch(const TcPlan* p, cudaStream_t stream, unsigned int* status);
+
+// Element-wise kernels.
+cudaError_t convert_f32_to_bf16(const float* src, __nv_bfloat16* dst, size_t n, cudaStream_t s);
+cudaError_t convert_bf16_to_f32(const __nv_bfloat16* src, float* dst, size_t n, cudaStream_t s);
+// dz = y (ref) or (y - t) * inv_batch (baseline); loss += 0.5 * sum(d^2) * loss_scale
+cudaError_t loss_grad_launch(const float* y, const float* target, void* dz, int dz_type, size_t n,
+                             int baseline, float inv_batch, double loss_scale, double* loss,
+                             cudaStream_t s);
+// w = fma(-lr, g, w); optional bf16 copy of the new weights
+cudaError_t sgd_launch(float* w, const void* g, int g_type, __nv_bfloat16* w_bf16, size_t n, float lr,
+                       int sm_count, cudaStream_t s);
+cudaError_t fill_uniform_launch(void* buf, int type, size_t n, uint64_t seed, float lo, float hi,
+                                cudaStream_t s);
+
+}  // namespace b2

@@ -1,0 +1,964 @@
+// Handle, step schedule and C ABI of b200mlp (see include/b200mlp.h).
+//
+// One handle = one GPU = one "socket" of the reference.  The step mirrors the loop
+// body of mlp_omp.cc:435-737 and the dependency graph of mlp_tbb.cc:1288-1367:
+//
+//   main stream   fwd(0) .. fwd(L-1), output gradient,
+//                 then for l = L-1 .. 0:  wgrad(l), dgrad(l)
+//   side stream   for l = L-1 .. 0:  [after wgrad(l)] allreduce(dW[l]),
+//                 [after dgrad(l), which still reads W[l]] SGD(l)
+//
+// and fwd(l) of the next step waits for SGD(l) only, so the reduction and update of
+// a layer overlap the backward GEMMs of the layers below it and, for the first
+// layers, the start of the next forward pass (the reference overlaps the same way
+// by dedicating threads: mlp_omp.cc:520-527,601-615,692-723).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "../../include/b200mlp.h"
+#include "common.cuh"
+#include "nccl_dyn.h"
+
+using namespace b2;
+
+namespace {
+
+thread_local std::string g_tls_error;
+
+struct Site {
+  GemmDesc d;
+  TcPlan* plan = nullptr;  // null: CUDA-core kernel
+  bool active = false;
+};
+
+}  // namespace
+
+struct b2_handle {
+  b2_config cfg;
+  std::vector<int> nf;
+  int L = 0, b0 = 0, b1 = 0, bl = 0, sms = 148;
+  int op_type = T_F32;    // element type of GEMM operands held on the device
+  int grad_type = T_F32;  // element type of dW
+  cudaStream_t s_main = nullptr, s_comm = nullptr;
+  std::vector<float*> w;
+  std::vector<__nv_bfloat16*> w16;
+  std::vector<void*> dw, act, dz;
+  float* y = nullptr;
+  float* target = nullptr;
+  void* dinput = nullptr;
+  float* stage = nullptr;  // fp32 staging for converted up/downloads
+  size_t stage_elems = 0;
+  double* loss_dev = nullptr;
+  unsigned int* status_dev = nullptr;
+  std::vector<cudaEvent_t> ev_wgrad, ev_dgrad, ev_upd;
+  std::vector<char> upd_pending;
+  cudaEvent_t ev_t0 = nullptr, ev_t1 = nullptr, ev_join = nullptr, ev_fork = nullptr;
+  std::vector<cudaEvent_t> ev_phase;  // [iters][L][B2_T_NUM][2], alive during one b2_step call
+  int ev_iter = 0;                    // step of the current call the recorder is in
+  std::vector<Site> fwd, wgrad, dgrad;
+  ncclComm_t comm = nullptr;
+  std::vector<double> phase_ms;
+  double step_ms = 0;
+  long long steps = 0, launches = 0, tc_launches = 0;
+  cudaGraphExec_t graph_exec = nullptr;
+  std::string err;
+};
+
+namespace {
+
+int fail(b2_handle* h, int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  if (h) h->err = buf;
+  g_tls_error = buf;
+  return code;
+}
+
+#define CK(h, call)                                                                              \
+  do {                                                                                           \
+    cudaError_t e_ = (call);                                                                     \
+    if (e_ != cudaSuccess)                                                                       \
+      return fail(h, B2_ERR_CUDA, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__, \
+                  __LINE__);                                                                     \
+  } while (0)
+
+#define NCK(h, call)                                                                         \
+  do {                                                                                       \
+    int r_ = (call);                                                                         \
+    if (r_ != ncclSuccess)                                                                   \
+      return fail(h, B2_ERR_NCCL, "%s failed: %s", #call, nccl_api().GetErrorString(r_));    \
+  } while (0)
+
+size_t esize(int type) { return type == T_BF16 ? 2 : 4; }
+
+void batch_range(int batch, int world, int rank, int* b, int* e) {
+  // get_partition(work, socket, 1, 0), Partition.cc:34-51
+  int per = (batch + world - 1) / world;
+  int lo = rank * per < batch ? rank * per : batch;
+  int hi = lo + per < batch ? lo + per : batch;
+  *b = lo;
+  *e = hi;
+}
+
+int make_site(b2_handle* h, Site& s, bool want_tc) {
+  s.active = s.d.M > 0 && s.d.N > 0 && s.d.K > 0;
+  s.plan = nullptr;
+  if (!s.active || !want_tc) return B2_OK;
+  char why[128];
+  s.plan = gemm_tc_plan_create(s.d, h->sms, why, sizeof why);
+  return B2_OK;  // a refused plan silently means the CUDA-core kernel serves this site
+}
+
+int run_site(b2_handle* h, const Site& s, cudaStream_t st) {
+  if (!s.active) return B2_OK;
+  ++h->launches;
+  if (s.plan) {
+    ++h->tc_launches;
+    CK(h, gemm_tc_launch(s.plan, st, h->status_dev));
+  } else {
+    CK(h, gemm_simt_launch(s.d, st));
+  }
+  return B2_OK;
+}
+
+bool use_tc(const b2_handle* h) { return h->cfg.precision != B2_PREC_FP32 && !h->cfg.force_simt; }
+
+cudaEvent_t phase_ev(b2_handle* h, int l, int phase, int end) {
+  return h->ev_phase[(((size_t)h->ev_iter * h->L + l) * B2_T_NUM + phase) * 2 + end];
+}
+
+int check_status(b2_handle* h) {
+  unsigned int st = 0;
+  CK(h, cudaMemcpy(&st, h->status_dev, sizeof st, cudaMemcpyDeviceToHost));
+  if (st != 0) {
+    cudaMemset(h->status_dev, 0, sizeof st);
+    return fail(h, B2_ERR_TIMEOUT, "tensor-core GEMM gave up waiting on a pipeline barrier (role %u)", st);
+  }
+  return B2_OK;
+}
+
+// Host (ld) <-> dense device matrix of `type`, through the fp32 staging buffer when
+// the device holds bf16.
+int upload_matrix(b2_handle* h, void* dev, int type, const float* host, size_t ld, int rows, int cols) {
+  if (rows <= 0 || cols <= 0) return B2_OK;
+  if (type == T_F32) {
+    CK(h, cudaMemcpy2DAsync(dev, (size_t)cols * 4, host, ld * 4, (size_t)cols * 4, rows, cudaMemcpyHostToDevice,
+                            h->s_main));
+  } else {
+    if ((size_t)rows * cols > h->stage_elems) return fail(h, B2_ERR_INVALID, "staging buffer too small");
+    CK(h, cudaMemcpy2DAsync(h->stage, (size_t)cols * 4, host, ld * 4, (size_t)cols * 4, rows,
+                            cudaMemcpyHostToDevice, h->s_main));
+    CK(h, convert_f32_to_bf16(h->stage, (__nv_bfloat16*)dev, (size_t)rows * cols, h->s_main));
+    ++h->launches;
+  }
+  return B2_OK;
+}
+
+int download_matrix(b2_handle* h, const void* dev, int type, float* host, size_t ld, int rows, int cols) {
+  if (rows <= 0 || cols <= 0) return B2_OK;
+  const void* src = dev;
+  if (type == T_BF16) {
+    if ((size_t)rows * cols > h->stage_elems) return fail(h, B2_ERR_INVALID, "staging buffer too small");
+    CK(h, convert_bf16_to_f32((const __nv_bfloat16*)dev, h->stage, (size_t)rows * cols, h->s_main));
+    ++h->launches;
+    src = h->stage;
+  }
+  CK(h, cudaMemcpy2DAsync(host, ld * 4, src, (size_t)cols * 4, (size_t)cols * 4, rows, cudaMemcpyDeviceToHost,
+                          h->s_main));
+  CK(h, cudaStreamSynchronize(h->s_main));
+  return B2_OK;
+}
+
+int build_sites(b2_handle* h) {
+  const int L = h->L, bl = h->bl;
+  const bool baseline = h->cfg.mode == B2_MODE_BASELINE;
+  const bool tc = use_tc(h);
+  h->fwd.assign(L, Site());
+  h->wgrad.assign(L, Site());
+  h->dgrad.assign(L, Site());
+  for (int l = 0; l < L; ++l) {
+    const int fi = h->nf[l], fo = h->nf[l + 1];
+    const void* wop = h->op_type == T_BF16 ? (const void*)h->w16[l] : (const void*)h->w[l];
+    // forward: A[l+1] = A[l] * W[l]^T (mlp_omp.cc:474-488)
+    GemmDesc f{};
+    f.M = bl; f.N = fo; f.K = fi;
+    f.A = h->act[l]; f.sAm = fi; f.sAk = 1;
+    f.B = wop; f.sBk = 1; f.sBn = fi;
+    f.C = (l == L - 1) ? (void*)h->y : h->act[l + 1];
+    f.ldc = fo;
+    f.alpha = 1.f; f.beta = 0.f;
+    f.epilogue = (baseline && l < L - 1) ? EPI_RELU : EPI_NONE;
+    f.in_type = h->op_type;
+    f.out_type = (l == L - 1) ? T_F32 : h->op_type;
+    h->fwd[l].d = f;
+    make_site(h, h->fwd[l], tc);
+    // weight gradient: dW[l] = dZ[l]^T * A[l] over this rank's rows (mlp_omp.cc:565-580)
+    GemmDesc g{};
+    g.M = fo; g.N = fi; g.K = bl;
+    g.A = h->dz[l]; g.sAm = 1; g.sAk = fo;
+    g.B = h->act[l]; g.sBk = fi; g.sBn = 1;
+    g.C = h->dw[l]; g.ldc = fi;
+    g.alpha = 1.f; g.beta = 0.f;
+    g.epilogue = EPI_NONE;
+    g.in_type = h->op_type;
+    g.out_type = h->grad_type;
+    h->wgrad[l].d = g;
+    make_site(h, h->wgrad[l], tc);
+    // input gradient: dA[l] = dZ[l] * W[l] (mlp_omp.cc:655-671), masked by ReLU'(A[l])
+    GemmDesc b{};
+    b.M = bl; b.N = fi; b.K = fo;
+    b.A = h->dz[l]; b.sAm = fo; b.sAk = 1;
+    b.B = wop; b.sBk = fi; b.sBn = 1;
+    b.C = (l == 0) ? h->dinput : h->dz[l - 1];
+    b.ldc = fi;
+    b.alpha = 1.f; b.beta = 0.f;
+    b.epilogue = (baseline && l > 0) ? EPI_MASK : EPI_NONE;
+    b.aux = h->act[l]; b.ldaux = fi;
+    b.in_type = h->op_type;
+    b.out_type = h->op_type;
+    h->dgrad[l].d = b;
+    make_site(h, h->dgrad[l], tc);
+    if (l == 0 && !h->cfg.input_grad) h->dgrad[l].active = false;
+  }
+  return B2_OK;
+}
+
+int layer_update(b2_handle* h, int l, cudaStream_t st, bool timed) {
+  const size_t n = (size_t)h->nf[l + 1] * h->nf[l];
+  if (h->cfg.world_size > 1 && h->cfg.allreduce) {
+    if (timed) CK(h, cudaEventRecord(phase_ev(h, l, B2_T_ALLREDUCE, 0), st));
+    NCK(h, nccl_api().AllReduce(h->dw[l], h->dw[l], n, h->grad_type == T_BF16 ? ncclBfloat16 : ncclFloat32,
+                                ncclSum, h->comm, st));
+    if (timed) CK(h, cudaEventRecord(phase_ev(h, l, B2_T_ALLREDUCE, 1), st));
+  }
+  return B2_OK;
+}
+
+int layer_sgd(b2_handle* h, int l, cudaStream_t st, bool timed) {
+  const size_t n = (size_t)h->nf[l + 1] * h->nf[l];
+  if (timed) CK(h, cudaEventRecord(phase_ev(h, l, B2_T_WGT_UPDATE, 0), st));
+  CK(h, sgd_launch(h->w[l], h->dw[l], h->grad_type, h->op_type == T_BF16 ? h->w16[l] : nullptr, n, h->cfg.lr,
+                   h->sms, st));
+  ++h->launches;
+  if (timed) CK(h, cudaEventRecord(phase_ev(h, l, B2_T_WGT_UPDATE, 1), st));
+  return B2_OK;
+}
+
+// Enqueue one training step on the two streams (no host synchronisation).
+int enqueue_step(b2_handle* h, bool timed) {
+  const int L = h->L;
+  const bool overlap = h->cfg.overlap != 0;
+  cudaStream_t sm = h->s_main, sc = overlap ? h->s_comm : h->s_main;
+  int rc;
+  CK(h, cudaMemsetAsync(h->loss_dev, 0, sizeof(double), sm));
+  for (int l = 0; l < L; ++l) {
+    if (overlap && h->upd_pending[l]) {
+      CK(h, cudaStreamWaitEvent(sm, h->ev_upd[l], 0));
+      h->upd_pending[l] = 0;
+    }
+    if (timed) CK(h, cudaEventRecord(phase_ev(h, l, B2_T_FWD, 0), sm));
+    if ((rc = run_site(h, h->fwd[l], sm))) return rc;
+    if (timed) CK(h, cudaEventRecord(phase_ev(h, l, B2_T_FWD, 1), sm));
+  }
+  {
+    const size_t n = (size_t)h->bl * h->nf[L];
+    const bool baseline = h->cfg.mode == B2_MODE_BASELINE;
+    CK(h, loss_grad_launch(h->y, h->target, h->dz[L - 1], h->op_type, n, baseline ? 1 : 0,
+                           1.0f / (float)h->cfg.batch, baseline ? 1.0 / (double)h->cfg.batch : 1.0, h->loss_dev,
+                           sm));
+    if (n) ++h->launches;
+  }
+  for (int l = L - 1; l >= 0; --l) {
+    if (timed) CK(h, cudaEventRecord(phase_ev(h, l, B2_T_WGT_GRAD, 0), sm));
+    if (h->wgrad[l].active) {
+      if ((rc = run_site(h, h->wgrad[l], sm))) return rc;
+    } else {  // a rank without batch rows contributes a zero gradient
+      CK(h, cudaMemsetAsync(h->dw[l], 0, (size_t)h->nf[l + 1] * h->nf[l] * esize(h->grad_type), sm));
+    }
+    if (timed) CK(h, cudaEventRecord(phase_ev(h, l, B2_T_WGT_GRAD, 1), sm));
+    if (overlap) {
+      CK(h, cudaEventRecord(h->ev_wgrad[l], sm));
+      CK(h, cudaStreamWaitEvent(sc, h->ev_wgrad[l], 0));
+    }
+    if ((rc = layer_update(h, l, sc, timed))) return rc;
+    if (timed) CK(h, cudaEventRecord(phase_ev(h, l, B2_T_BWD, 0), sm));
+    if ((rc = run_site(h, h->dgrad[l], sm))) return rc;
+    if (timed) CK(h, cudaEventRecord(phase_ev(h, l, B2_T_BWD, 1), sm));
+    if (overlap) {
+      CK(h, cudaEventRecord(h->ev_dgrad[l], sm));
+      CK(h, cudaStreamWaitEvent(sc, h->ev_dgrad[l], 0));
+    }
+    if ((rc = layer_sgd(h, l, sc, timed))) return rc;
+    if (overlap) {
+      CK(h, cudaEventRecord(h->ev_upd[l], sc));
+      h->upd_pending[l] = 1;
+    }
+  }
+  return B2_OK;
+}
+
+int join_streams(b2_handle* h) {
+  if (h->cfg.overlap) {
+    CK(h, cudaEventRecord(h->ev_join, h->s_comm));
+    CK(h, cudaStreamWaitEvent(h->s_main, h->ev_join, 0));
+    for (auto& p : h->upd_pending) p = 0;
+  }
+  return B2_OK;
+}
+
+void free_all(b2_handle* h) {
+  if (!h) return;
+  cudaSetDevice(h->cfg.device);
+  if (h->s_main) cudaStreamSynchronize(h->s_main);
+  if (h->s_comm) cudaStreamSynchronize(h->s_comm);
+  if (h->comm && nccl_api().ok) nccl_api().CommDestroy(h->comm);
+  if (h->graph_exec) cudaGraphExecDestroy(h->graph_exec);
+  for (auto& s : h->fwd) gemm_tc_plan_destroy(s.plan);
+  for (auto& s : h->wgrad) gemm_tc_plan_destroy(s.plan);
+  for (auto& s : h->dgrad) gemm_tc_plan_destroy(s.plan);
+  for (auto p : h->w) cudaFree(p);
+  for (auto p : h->w16) cudaFree(p);
+  for (auto p : h->dw) cudaFree(p);
+  for (auto p : h->act) cudaFree(p);
+  for (auto p : h->dz) cudaFree(p);
+  cudaFree(h->y);
+  cudaFree(h->target);
+  cudaFree(h->dinput);
+  cudaFree(h->stage);
+  cudaFree(h->loss_dev);
+  cudaFree(h->status_dev);
+  for (auto e : h->ev_wgrad) cudaEventDestroy(e);
+  for (auto e : h->ev_dgrad) cudaEventDestroy(e);
+  for (auto e : h->ev_upd) cudaEventDestroy(e);
+  for (auto e : h->ev_phase)
+    if (e) cudaEventDestroy(e);
+  if (h->ev_t0) cudaEventDestroy(h->ev_t0);
+  if (h->ev_t1) cudaEventDestroy(h->ev_t1);
+  if (h->ev_join) cudaEventDestroy(h->ev_join);
+  if (h->ev_fork) cudaEventDestroy(h->ev_fork);
+  if (h->s_main) cudaStreamDestroy(h->s_main);
+  if (h->s_comm) cudaStreamDestroy(h->s_comm);
+  delete h;
+}
+
+template <typename T>
+int dev_alloc(b2_handle* h, T** p, size_t bytes) {
+  *p = nullptr;
+  if (bytes == 0) bytes = 16;
+  CK(h, cudaMalloc((void**)p, bytes));
+  CK(h, cudaMemset(*p, 0, bytes));
+  return B2_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int b2_config_default(b2_config* c) {
+  if (!c) return B2_ERR_INVALID;
+  memset(c, 0, sizeof *c);
+  c->world_size = 1;
+  c->mode = B2_MODE_BASELINE;
+  c->precision = B2_PREC_FP32;
+  c->allreduce = 1;
+  c->overlap = 1;
+  c->input_grad = 1;
+  c->lr = 0.01f;
+  return B2_OK;
+}
+
+const char* b2_version(void) { return "b200mlp 0.1 (sm_100a)"; }
+
+const char* b2_last_error(const b2_handle* h) { return h ? h->err.c_str() : g_tls_error.c_str(); }
+
+int b2_nccl_unique_id(void* out) {
+  if (!out) return fail(nullptr, B2_ERR_INVALID, "null output");
+  NcclApi& n = nccl_api();
+  if (!n.ok) return fail(nullptr, B2_ERR_NCCL, "%s", n.error.c_str());
+  ncclUniqueId id;
+  NCK(nullptr, n.GetUniqueId(&id));
+  memcpy(out, &id, sizeof id);
+  return B2_OK;
+}
+
+int b2_create(const b2_config* cfg, b2_handle** out) {
+  if (!cfg || !out) return fail(nullptr, B2_ERR_INVALID, "null argument");
+  *out = nullptr;
+  if (cfg->nlayers < 1 || !cfg->nfeatures) return fail(nullptr, B2_ERR_INVALID, "nlayers/nfeatures");
+  if (cfg->batch < 1) return fail(nullptr, B2_ERR_INVALID, "batch must be positive");
+  if (cfg->world_size < 1 || cfg->rank < 0 || cfg->rank >= cfg->world_size)
+    return fail(nullptr, B2_ERR_INVALID, "rank %d outside world of %d", cfg->rank, cfg->world_size);
+  if (cfg->precision < B2_PREC_FP32 || cfg->precision > B2_PREC_BF16)
+    return fail(nullptr, B2_ERR_INVALID, "unknown precision %d", cfg->precision);
+  if (cfg->mode != B2_MODE_REF && cfg->mode != B2_MODE_BASELINE)
+    return fail(nullptr, B2_ERR_INVALID, "unknown mode %d", cfg->mode);
+  if (cfg->grad_bf16 && cfg->precision != B2_PREC_BF16)
+    return fail(nullptr, B2_ERR_INVALID, "grad_bf16 needs BF16 precision");
+  for (int i = 0; i <= cfg->nlayers; ++i)
+    if (cfg->nfeatures[i] < 1) return fail(nullptr, B2_ERR_INVALID, "nfeatures[%d] must be positive", i);
+  if (cfg->world_size > 1 && cfg->allreduce && !cfg->nccl_unique_id)
+    return fail(nullptr, B2_ERR_INVALID, "world_size > 1 needs nccl_unique_id");
+
+  int ndev = 0;
+  cudaError_t e = cudaGetDeviceCount(&ndev);
+  if (e != cudaSuccess || ndev == 0)
+    return fail(nullptr, B2_ERR_CUDA, "no CUDA device (%s); this library has no CPU path",
+                e == cudaSuccess ? "count 0" : cudaGetErrorString(e));
+  if (cfg->device < 0 || cfg->device >= ndev) return fail(nullptr, B2_ERR_INVALID, "device %d of %d", cfg->device, ndev);
+
+  b2_handle* h = new b2_handle();
+  h->cfg = *cfg;
+  h->L = cfg->nlayers;
+  h->nf.assign(cfg->nfeatures, cfg->nfeatures + cfg->nlayers + 1);
+  h->cfg.nfeatures = h->nf.data();
+  h->cfg.nccl_unique_id = nullptr;
+  batch_range(cfg->batch, cfg->world_size, cfg->rank, &h->b0, &h->b1);
+  h->bl = h->b1 - h->b0;
+  h->op_type = cfg->precision == B2_PREC_BF16 ? T_BF16 : T_F32;
+  h->grad_type = cfg->grad_bf16 ? T_BF16 : T_F32;
+  int rc = B2_OK;
+#define TRY(x)            \
+  do {                    \
+    rc = (x);             \
+    if (rc != B2_OK) {    \
+      g_tls_error = h->err; \
+      free_all(h);        \
+      return rc;          \
+    }                     \
+  } while (0)
+#define TRYCK(call)                                                                                  \
+  do {                                                                                               \
+    cudaError_t e_ = (call);                                                                         \
+    if (e_ != cudaSuccess) {                                                                         \
+      rc = fail(h, B2_ERR_CUDA, "%s failed: %s", #call, cudaGetErrorString(e_));                     \
+      free_all(h);                                                                                   \
+      return rc;                                                                                     \
+    }                                                                                                \
+  } while (0)
+
+  TRYCK(cudaSetDevice(cfg->device));
+  cudaDeviceProp prop;
+  TRYCK(cudaGetDeviceProperties(&prop, cfg->device));
+  if (prop.major != 10)
+    TRY(fail(h, B2_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only", cfg->device,
+             prop.major, prop.minor));
+  h->sms = prop.multiProcessorCount;
+  TRYCK(cudaStreamCreateWithFlags(&h->s_main, cudaStreamNonBlocking));
+  TRYCK(cudaStreamCreateWithFlags(&h->s_comm, cudaStreamNonBlocking));
+
+  const int L = h->L;
+  const size_t bl = (size_t)h->bl;
+  h->w.assign(L, nullptr);
+  h->w16.assign(L, nullptr);
+  h->dw.assign(L, nullptr);
+  h->dz.assign(L, nullptr);
+  h->act.assign(L + 1, nullptr);
+  size_t max_elems = 16;
+  for (int l = 0; l < L; ++l) {
+    const size_t nw = (size_t)h->nf[l + 1] * h->nf[l];
+    TRY(dev_alloc(h, &h->w[l], nw * 4));
+    if (h->op_type == T_BF16) TRY(dev_alloc(h, &h->w16[l], nw * 2));
+    TRY(dev_alloc(h, &h->dw[l], nw * esize(h->grad_type)));
+    TRY(dev_alloc(h, &h->dz[l], bl * h->nf[l + 1] * esize(h->op_type)));
+    TRY(dev_alloc(h, &h->act[l], bl * h->nf[l] * esize(h->op_type)));
+    if (nw > max_elems) max_elems = nw;
+    if (bl * h->nf[l] > max_elems) max_elems = bl * h->nf[l];
+    if (bl * h->nf[l + 1] > max_elems) max_elems = bl * h->nf[l + 1];
+  }
+  TRY(dev_alloc(h, &h->y, bl * h->nf[L] * 4));
+  TRY(dev_alloc(h, &h->target, bl * h->nf[L] * 4));
+  TRY(dev_alloc(h, &h->dinput, bl * h->nf[0] * esize(h->op_type)));
+  if (h->op_type == T_BF16 || h->grad_type == T_BF16) {
+    h->stage_elems = max_elems;
+    TRY(dev_alloc(h, &h->stage, max_elems * 4));
+  }
+  TRY(dev_alloc(h, &h->loss_dev, sizeof(double)));
+  TRY(dev_alloc(h, &h->status_dev, sizeof(unsigned int)));
+
+  h->ev_wgrad.assign(L, nullptr);
+  h->ev_dgrad.assign(L, nullptr);
+  h->ev_upd.assign(L, nullptr);
+  h->upd_pending.assign(L, 0);
+  for (int l = 0; l < L; ++l) {
+    TRYCK(cudaEventCreateWithFlags(&h->ev_wgrad[l], cudaEventDisableTiming));
+    TRYCK(cudaEventCreateWithFlags(&h->ev_dgrad[l], cudaEventDisableTiming));
+    TRYCK(cudaEventCreateWithFlags(&h->ev_upd[l], cudaEventDisableTiming));
+  }
+  TRYCK(cudaEventCreate(&h->ev_t0));
+  TRYCK(cudaEventCreate(&h->ev_t1));
+  TRYCK(cudaEventCreateWithFlags(&h->ev_join, cudaEventDisableTiming));
+  TRYCK(cudaEventCreateWithFlags(&h->ev_fork, cudaEventDisableTiming));
+  h->phase_ms.assign((size_t)L * B2_T_NUM, 0.0);
+
+  if (cfg->world_size > 1 && cfg->allreduce) {
+    NcclApi& n = nccl_api();
+    if (!n.ok) TRY(fail(h, B2_ERR_NCCL, "%s", n.error.c_str()));
+    ncclUniqueId id;
+    memcpy(&id, cfg->nccl_unique_id, sizeof id);
+    int r = n.CommInitRank(&h->comm, cfg->world_size, id, cfg->rank);
+    if (r != ncclSuccess) TRY(fail(h, B2_ERR_NCCL, "ncclCommInitRank failed: %s", n.GetErrorString(r)));
+  }
+  TRY(build_sites(h));
+  TRYCK(cudaDeviceSynchronize());
+#undef TRY
+#undef TRYCK
+  *out = h;
+  return B2_OK;
+}
+
+int b2_destroy(b2_handle* h) {
+  free_all(h);
+  return B2_OK;
+}
+
+int b2_batch_range(const b2_handle* h, int* begin, int* end) {
+  if (!h) return B2_ERR_INVALID;
+  if (begin) *begin = h->b0;
+  if (end) *end = h->b1;
+  return B2_OK;
+}
+
+#define ENTER(h)                                                \
+  if (!(h)) return fail(nullptr, B2_ERR_INVALID, "null handle"); \
+  CK(h, cudaSetDevice((h)->cfg.device))
+
+#define LAYER_OK(h, l, hi) \
+  if ((l) < 0 || (l) > (hi)) return fail(h, B2_ERR_INVALID, "layer %d out of range", (l))
+
+int b2_upload_weights(b2_handle* h, int l, const float* host, size_t ld) {
+  ENTER(h);
+  LAYER_OK(h, l, h->L - 1);
+  if (!host || ld < (size_t)h->nf[l]) return fail(h, B2_ERR_INVALID, "bad host matrix");
+  const int rows = h->nf[l + 1], cols = h->nf[l];
+  CK(h, cudaMemcpy2DAsync(h->w[l], (size_t)cols * 4, host, ld * 4, (size_t)cols * 4, rows, cudaMemcpyHostToDevice,
+                          h->s_main));
+  if (h->op_type == T_BF16) {
+    CK(h, convert_f32_to_bf16(h->w[l], h->w16[l], (size_t)rows * cols, h->s_main));
+    ++h->launches;
+  }
+  CK(h, cudaStreamSynchronize(h->s_main));
+  return B2_OK;
+}
+
+int b2_download_weights(b2_handle* h, int l, float* host, size_t ld) {
+  ENTER(h);
+  LAYER_OK(h, l, h->L - 1);
+  if (!host || ld < (size_t)h->nf[l]) return fail(h, B2_ERR_INVALID, "bad host matrix");
+  return download_matrix(h, h->w[l], T_F32, host, ld, h->nf[l + 1], h->nf[l]);
+}
+
+int b2_upload_input(b2_handle* h, const float* host, size_t ld) {
+  ENTER(h);
+  if (!host || ld < (size_t)h->nf[0]) return fail(h, B2_ERR_INVALID, "bad host matrix");
+  int rc = upload_matrix(h, h->act[0], h->op_type, host + (size_t)h->b0 * ld, ld, h->bl, h->nf[0]);
+  if (rc) return rc;
+  CK(h, cudaStreamSynchronize(h->s_main));
+  return B2_OK;
+}
+
+int b2_upload_target(b2_handle* h, const float* host, size_t ld) {
+  ENTER(h);
+  if (!host || ld < (size_t)h->nf[h->L]) return fail(h, B2_ERR_INVALID, "bad host matrix");
+  int rc = upload_matrix(h, h->target, T_F32, host + (size_t)h->b0 * ld, ld, h->bl, h->nf[h->L]);
+  if (rc) return rc;
+  CK(h, cudaStreamSynchronize(h->s_main));
+  return B2_OK;
+}
+
+int b2_download_activation(b2_handle* h, int l, float* host, size_t ld) {
+  ENTER(h);
+  LAYER_OK(h, l, h->L);
+  if (!host || ld < (size_t)h->nf[l]) return fail(h, B2_ERR_INVALID, "bad host matrix");
+  if (l == h->L) return download_matrix(h, h->y, T_F32, host + (size_t)h->b0 * ld, ld, h->bl, h->nf[l]);
+  return download_matrix(h, h->act[l], h->op_type, host + (size_t)h->b0 * ld, ld, h->bl, h->nf[l]);
+}
+
+int b2_download_dz(b2_handle* h, int l, float* host, size_t ld) {
+  ENTER(h);
+  LAYER_OK(h, l, h->L - 1);
+  if (!host || ld < (size_t)h->nf[l + 1]) return fail(h, B2_ERR_INVALID, "bad host matrix");
+  return download_matrix(h, h->dz[l], h->op_type, host + (size_t)h->b0 * ld, ld, h->bl, h->nf[l + 1]);
+}
+
+int b2_download_input_grad(b2_handle* h, float* host, size_t ld) {
+  ENTER(h);
+  if (!host || ld < (size_t)h->nf[0]) return fail(h, B2_ERR_INVALID, "bad host matrix");
+  return download_matrix(h, h->dinput, h->op_type, host + (size_t)h->b0 * ld, ld, h->bl, h->nf[0]);
+}
+
+int b2_download_weight_grad(b2_handle* h, int l, float* host, size_t ld) {
+  ENTER(h);
+  LAYER_OK(h, l, h->L - 1);
+  if (!host || ld < (size_t)h->nf[l]) return fail(h, B2_ERR_INVALID, "bad host matrix");
+  return download_matrix(h, h->dw[l], h->grad_type, host, ld, h->nf[l + 1], h->nf[l]);
+}
+
+int b2_upload_weight_grad(b2_handle* h, int l, const float* host, size_t ld) {
+  ENTER(h);
+  LAYER_OK(h, l, h->L - 1);
+  if (!host || ld < (size_t)h->nf[l]) return fail(h, B2_ERR_INVALID, "bad host matrix");
+  int rc = upload_matrix(h, h->dw[l], h->grad_type, host, ld, h->nf[l + 1], h->nf[l]);
+  if (rc) return rc;
+  CK(h, cudaStreamSynchronize(h->s_main));
+  return B2_OK;
+}
+
+int b2_set_lr(b2_handle* h, float lr) {
+  if (!h) return B2_ERR_INVALID;
+  if (h->graph_exec) {  // the step graph has the old value baked in
+    cudaGraphExecDestroy(h->graph_exec);
+    h->graph_exec = nullptr;
+  }
+  h->cfg.lr = lr;
+  return B2_OK;
+}
+
+int b2_sync(b2_handle* h) {
+  ENTER(h);
+  CK(h, cudaStreamSynchronize(h->s_main));
+  CK(h, cudaStreamSynchronize(h->s_comm));
+  return check_status(h);
+}
+
+static int capture_graph(b2_handle* h) {
+  cudaGraph_t graph = nullptr;
+  CK(h, cudaStreamBeginCapture(h->s_main, cudaStreamCaptureModeThreadLocal));
+  int rc = B2_OK;
+  if (h->cfg.overlap) {  // fork the side stream into the capture
+    cudaEventRecord(h->ev_fork, h->s_main);
+    cudaStreamWaitEvent(h->s_comm, h->ev_fork, 0);
+  }
+  for (auto& p : h->upd_pending) p = 0;
+  const long long l0 = h->launches, t0 = h->tc_launches;
+  rc = enqueue_step(h, false);
+  if (rc == B2_OK) rc = join_streams(h);
+  h->launches = l0;  // launches are counted per replay
+  h->tc_launches = t0;
+  cudaError_t e = cudaStreamEndCapture(h->s_main, &graph);
+  if (rc != B2_OK) {
+    if (graph) cudaGraphDestroy(graph);
+    return rc;
+  }
+  if (e != cudaSuccess) return fail(h, B2_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
+  e = cudaGraphInstantiate(&h->graph_exec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (e != cudaSuccess) return fail(h, B2_ERR_CUDA, "cudaGraphInstantiate failed: %s", cudaGetErrorString(e));
+  return B2_OK;
+}
+
+static long long launches_per_step(const b2_handle* h, long long* tc) {
+  long long n = 0, t = 0;
+  for (int l = 0; l < h->L; ++l) {
+    for (const Site* s : {&h->fwd[l], &h->wgrad[l], &h->dgrad[l]})
+      if (s->active) {
+        ++n;
+        if (s->plan) ++t;
+      }
+    ++n;  // SGD
+  }
+  if ((size_t)h->bl * h->nf[h->L]) ++n;  // output gradient
+  if (tc) *tc = t;
+  return n;
+}
+
+int b2_step(b2_handle* h, int iters) {
+  ENTER(h);
+  if (iters < 0) return fail(h, B2_ERR_INVALID, "iters < 0");
+  if (iters == 0) return B2_OK;
+  const bool timed = h->cfg.collect_timing != 0;
+  const bool graph = h->cfg.use_graph && !timed;
+  int rc;
+  if (graph && !h->graph_exec) {
+    CK(h, cudaStreamSynchronize(h->s_main));
+    CK(h, cudaStreamSynchronize(h->s_comm));
+    if ((rc = capture_graph(h))) return rc;
+  }
+  if (timed) {  // one event pair per (step, layer, phase): nothing is read back before the end
+    h->ev_phase.assign((size_t)iters * h->L * B2_T_NUM * 2, nullptr);
+    for (auto& ev : h->ev_phase) CK(h, cudaEventCreate(&ev));
+  }
+  CK(h, cudaEventRecord(h->ev_t0, h->s_main));
+  for (int it = 0; it < iters; ++it) {
+    if (graph) {
+      CK(h, cudaGraphLaunch(h->graph_exec, h->s_main));
+      long long t = 0;
+      h->launches += launches_per_step(h, &t);
+      h->tc_launches += t;
+    } else {
+      h->ev_iter = it;
+      if ((rc = enqueue_step(h, timed))) return rc;
+    }
+  }
+  if (!graph && (rc = join_streams(h))) return rc;
+  CK(h, cudaEventRecord(h->ev_t1, h->s_main));
+  CK(h, cudaStreamSynchronize(h->s_main));
+  CK(h, cudaStreamSynchronize(h->s_comm));
+  float ms = 0.f;
+  CK(h, cudaEventElapsedTime(&ms, h->ev_t0, h->ev_t1));
+  h->step_ms += ms;
+  h->steps += iters;
+  if (timed) {
+    for (int it = 0; it < iters; ++it) {
+      h->ev_iter = it;
+      for (int l = 0; l < h->L; ++l)
+        for (int ph = 0; ph < B2_T_NUM; ++ph) {
+          float pm = 0.f;
+          if (cudaEventElapsedTime(&pm, phase_ev(h, l, ph, 0), phase_ev(h, l, ph, 1)) == cudaSuccess)
+            h->phase_ms[(size_t)l * B2_T_NUM + ph] += pm;
+          else
+            cudaGetLastError();  // phase not recorded in this configuration (e.g. no allreduce)
+        }
+    }
+    for (auto ev : h->ev_phase) cudaEventDestroy(ev);
+    h->ev_phase.clear();
+    h->ev_iter = 0;
+  }
+  return check_status(h);
+}
+
+int b2_loss(b2_handle* h, double* loss) {
+  ENTER(h);
+  if (!loss) return fail(h, B2_ERR_INVALID, "null output");
+  CK(h, cudaMemcpyAsync(loss, h->loss_dev, sizeof(double), cudaMemcpyDeviceToHost, h->s_main));
+  CK(h, cudaStreamSynchronize(h->s_main));
+  return B2_OK;
+}
+
+int b2_train_step_host(b2_handle* h, const float* x, size_t ldx, const float* t, size_t ldt, double* loss) {
+  ENTER(h);
+  if (!x || ldx < (size_t)h->nf[0]) return fail(h, B2_ERR_INVALID, "bad input matrix");
+  int rc;
+  // fwd(0) of this step must not start before the copy; the copy must not start
+  // before the previous step stopped reading act[0] - both hold on the main stream.
+  if ((rc = upload_matrix(h, h->act[0], h->op_type, x + (size_t)h->b0 * ldx, ldx, h->bl, h->nf[0]))) return rc;
+  if (t) {
+    if (ldt < (size_t)h->nf[h->L]) return fail(h, B2_ERR_INVALID, "bad target matrix");
+    if ((rc = upload_matrix(h, h->target, T_F32, t + (size_t)h->b0 * ldt, ldt, h->bl, h->nf[h->L]))) return rc;
+  }
+  if ((rc = b2_step(h, 1))) return rc;
+  if (loss) return b2_loss(h, loss);
+  return B2_OK;
+}
+
+int b2_host_alloc(void** ptr, size_t bytes) {
+  if (!ptr) return B2_ERR_INVALID;
+  cudaError_t e = cudaHostAlloc(ptr, bytes, cudaHostAllocDefault);
+  if (e != cudaSuccess) return fail(nullptr, B2_ERR_CUDA, "cudaHostAlloc: %s", cudaGetErrorString(e));
+  return B2_OK;
+}
+
+int b2_host_free(void* ptr) {
+  cudaError_t e = cudaFreeHost(ptr);
+  if (e != cudaSuccess) return fail(nullptr, B2_ERR_CUDA, "cudaFreeHost: %s", cudaGetErrorString(e));
+  return B2_OK;
+}
+
+int b2_allreduce_sgd(b2_handle* h, int l) {
+  ENTER(h);
+  LAYER_OK(h, l, h->L - 1);
+  int rc;
+  if ((rc = layer_update(h, l, h->s_main, false))) return rc;
+  if ((rc = layer_sgd(h, l, h->s_main, false))) return rc;
+  CK(h, cudaStreamSynchronize(h->s_main));
+  return B2_OK;
+}
+
+int b2_allreduce_bench(b2_handle* h, size_t count, int dtype, int warmup, int iters, double* ms_per_iter,
+                       double* checksum) {
+  ENTER(h);
+  if (count == 0 || iters < 1 || warmup < 0) return fail(h, B2_ERR_INVALID, "bad sweep arguments");
+  if (dtype != B2_DTYPE_F32 && dtype != B2_DTYPE_BF16) return fail(h, B2_ERR_INVALID, "bad dtype");
+  const int type = dtype == B2_DTYPE_BF16 ? T_BF16 : T_F32;
+  const int ntype = dtype == B2_DTYPE_BF16 ? ncclBfloat16 : ncclFloat32;
+  const bool multi = h->cfg.world_size > 1 && h->comm;
+  void *src = nullptr, *dst = nullptr;
+  CK(h, cudaMalloc(&src, count * esize(type)));
+  cudaError_t e = cudaMalloc(&dst, count * esize(type));
+  if (e != cudaSuccess) {
+    cudaFree(src);
+    return fail(h, B2_ERR_CUDA, "cudaMalloc: %s", cudaGetErrorString(e));
+  }
+  int rc = B2_OK;
+  auto run = [&]() -> int {
+    if (multi) {
+      NCK(h, nccl_api().AllReduce(src, dst, count, ntype, ncclSum, h->comm, h->s_main));
+    } else {
+      CK(h, cudaMemcpyAsync(dst, src, count * esize(type), cudaMemcpyDeviceToDevice, h->s_main));
+    }
+    return B2_OK;
+  };
+  do {
+    if (fill_uniform_launch(src, type, count, (uint64_t)h->cfg.rank, -1.f, 1.f, h->s_main) != cudaSuccess) {
+      rc = fail(h, B2_ERR_CUDA, "fill failed");
+      break;
+    }
+    ++h->launches;
+    for (int i = 0; i < warmup && rc == B2_OK; ++i) rc = run();
+    if (rc) break;
+    cudaEventRecord(h->ev_t0, h->s_main);
+    for (int i = 0; i < iters && rc == B2_OK; ++i) rc = run();
+    if (rc) break;
+    cudaEventRecord(h->ev_t1, h->s_main);
+    if (cudaStreamSynchronize(h->s_main) != cudaSuccess) {
+      rc = fail(h, B2_ERR_CUDA, "allreduce sweep: %s", cudaGetErrorString(cudaGetLastError()));
+      break;
+    }
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, h->ev_t0, h->ev_t1);
+    if (ms_per_iter) *ms_per_iter = (double)ms / iters;
+    if (checksum) {
+      const size_t n = count < 4096 ? count : 4096;
+      std::vector<float> host(n);
+      if (type == T_BF16) {
+        std::vector<__nv_bfloat16> hb(n);
+        cudaMemcpy(hb.data(), dst, n * 2, cudaMemcpyDeviceToHost);
+        for (size_t i = 0; i < n; ++i) host[i] = __bfloat162float(hb[i]);
+      } else {
+        cudaMemcpy(host.data(), dst, n * 4, cudaMemcpyDeviceToHost);
+      }
+      double s = 0;
+      for (size_t i = 0; i < n; ++i) s += host[i];
+      *checksum = s;
+    }
+  } while (0);
+  cudaFree(src);
+  cudaFree(dst);
+  return rc;
+}
+
+int b2_get_timing(b2_handle* h, double* phase_ms, double* step_ms, long long* steps) {
+  if (!h) return B2_ERR_INVALID;
+  if (phase_ms) memcpy(phase_ms, h->phase_ms.data(), h->phase_ms.size() * sizeof(double));
+  if (step_ms) *step_ms = h->step_ms;
+  if (steps) *steps = h->steps;
+  return B2_OK;
+}
+
+int b2_reset_timing(b2_handle* h) {
+  if (!h) return B2_ERR_INVALID;
+  std::fill(h->phase_ms.begin(), h->phase_ms.end(), 0.0);
+  h->step_ms = 0;
+  h->steps = 0;
+  return B2_OK;
+}
+
+int b2_launch_counts(const b2_handle* h, long long* total, long long* tc) {
+  if (!h) return B2_ERR_INVALID;
+  if (total) *total = h->launches;
+  if (tc) *tc = h->tc_launches;
+  return B2_OK;
+}
+
+static int gemm_common(b2_handle* h, int precision, GemmDesc& d, cudaStream_t st) {
+  TcPlan* plan = nullptr;
+  if (precision != B2_PREC_FP32 && !h->cfg.force_simt) {
+    char why[128];
+    plan = gemm_tc_plan_create(d, h->sms, why, sizeof why);
+  }
+  ++h->launches;
+  cudaError_t e;
+  if (plan) {
+    ++h->tc_launches;
+    e = gemm_tc_launch(plan, st, h->status_dev);
+    gemm_tc_plan_destroy(plan);  // the tensor maps were passed by value at launch
+  } else {
+    e = gemm_simt_launch(d, st);
+  }
+  if (e != cudaSuccess) return fail(h, B2_ERR_CUDA, "GEMM launch: %s", cudaGetErrorString(e));
+  return B2_OK;
+}
+
+int b2_sgemm(b2_handle* h, int precision, int transa, int transb, int m, int n, int k, float alpha, const float* a,
+             size_t lda, const float* b, size_t ldb, float beta, float* c, size_t ldc) {
+  ENTER(h);
+  if (precision == B2_PREC_BF16) return fail(h, B2_ERR_UNSUPPORTED, "b2_sgemm takes fp32 device operands");
+  if (m < 0 || n < 0 || k < 0 || !a || !b || !c) return fail(h, B2_ERR_INVALID, "bad GEMM arguments");
+  GemmDesc d{};
+  d.M = m; d.N = n; d.K = k;
+  d.A = a; d.sAm = transa ? 1 : (long long)lda; d.sAk = transa ? (long long)lda : 1;
+  d.B = b; d.sBk = transb ? 1 : (long long)ldb; d.sBn = transb ? (long long)ldb : 1;
+  d.C = c; d.ldc = (long long)ldc;
+  d.alpha = alpha; d.beta = beta;
+  d.epilogue = EPI_NONE;
+  d.in_type = T_F32; d.out_type = T_F32;
+  return gemm_common(h, precision, d, h->s_main);
+}
+
+int b2_sgemm_host(b2_handle* h, int precision, int transa, int transb, int m, int n, int k, const float* a,
+                  size_t lda, const float* b, size_t ldb, float* c, size_t ldc, int epilogue, const float* aux,
+                  size_t ldaux) {
+  ENTER(h);
+  if (m < 1 || n < 1 || k < 1 || !a || !b || !c) return fail(h, B2_ERR_INVALID, "bad GEMM arguments");
+  if (epilogue < EPI_NONE || epilogue > EPI_MASK) return fail(h, B2_ERR_INVALID, "bad epilogue");
+  if (epilogue == EPI_MASK && !aux) return fail(h, B2_ERR_INVALID, "mask epilogue needs aux");
+  const int in_type = precision == B2_PREC_BF16 ? T_BF16 : T_F32;
+  // like the step: bf16 operands produce bf16 activations/gradients, fp32 otherwise
+  const int out_type = (in_type == T_BF16 && epilogue != EPI_NONE) ? T_BF16 : T_F32;
+  const int ar = transa ? k : m, ac = transa ? m : k;
+  const int br = transb ? n : k, bc = transb ? k : n;
+  void *da = nullptr, *db = nullptr, *dc = nullptr, *dx = nullptr;
+  float* stage = nullptr;
+  size_t big = (size_t)ar * ac;
+  if ((size_t)br * bc > big) big = (size_t)br * bc;
+  if ((size_t)m * n > big) big = (size_t)m * n;
+  int rc = B2_OK;
+  auto put = [&](void** dev, const float* host, size_t ld, int rows, int cols) -> int {
+    CK(h, cudaMalloc(dev, (size_t)rows * cols * esize(in_type)));
+    if (in_type == T_F32) {
+      CK(h, cudaMemcpy2DAsync(*dev, (size_t)cols * 4, host, ld * 4, (size_t)cols * 4, rows, cudaMemcpyHostToDevice,
+                              h->s_main));
+    } else {
+      CK(h, cudaMemcpy2DAsync(stage, (size_t)cols * 4, host, ld * 4, (size_t)cols * 4, rows,
+                              cudaMemcpyHostToDevice, h->s_main));
+      CK(h, convert_f32_to_bf16(stage, (__nv_bfloat16*)*dev, (size_t)rows * cols, h->s_main));
+      CK(h, cudaStreamSynchronize(h->s_main));
+    }
+    return B2_OK;
+  };
+  do {
+    if (cudaMalloc((void**)&stage, big * 4) != cudaSuccess) { rc = fail(h, B2_ERR_CUDA, "cudaMalloc"); break; }
+    if ((rc = put(&da, a, lda, ar, ac))) break;
+    if ((rc = put(&db, b, ldb, br, bc))) break;
+    if (epilogue == EPI_MASK && (rc = put(&dx, aux, ldaux, m, n))) break;
+    if (cudaMalloc(&dc, (size_t)m * n * esize(out_type)) != cudaSuccess) { rc = fail(h, B2_ERR_CUDA, "cudaMalloc"); break; }
+    GemmDesc d{};
+    d.M = m; d.N = n; d.K = k;
+    d.A = da; d.sAm = transa ? 1 : ac; d.sAk = transa ? ac : 1;
+    d.B = db; d.sBk = transb ? 1 : bc; d.sBn = transb ? bc : 1;
+    d.C = dc; d.ldc = n;
+    d.aux = dx; d.ldaux = n;
+    d.alpha = 1.f; d.beta = 0.f;
+    d.epilogue = epilogue;
+    d.in_type = in_type; d.out_type = out_type;
+    if ((rc = gemm_common(h, precision, d, h->s_main))) break;
+    const void* src = dc;
+    if (out_type == T_BF16) {
+      if (convert_bf16_to_f32((const __nv_bfloat16*)dc, stage, (size_t)m * n, h->s_main) != cudaSuccess) {
+        rc = fail(h, B2_ERR_CUDA, "convert");
+        break;
+      }
+      src = stage;
+    }
+    if (cudaMemcpy2DAsync(c, ldc * 4, src, (size_t)n * 4, (size_t)n * 4, m, cudaMemcpyDeviceToHost, h->s_main) !=
+            cudaSuccess ||
+        cudaStreamSynchronize(h->s_main) != cudaSuccess) {
+      rc = fail(h, B2_ERR_CUDA, "GEMM readback: %s", cudaGetErrorString(cudaGetLastError()));
+      break;
+    }
+    rc = check_status(h);
+  } while (0);
+  cudaFree(da); cudaFree(db); cudaFree(dc); cudaFree(dx); cudaFree(stage);
+  return rc;
+}
+
+}  // extern "C"

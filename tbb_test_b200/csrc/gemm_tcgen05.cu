@@ -1,0 +1,572 @@
+// Tensor-core GEMM for sm_100a: TMA -> shared memory -> tcgen05.mma -> TMEM ->
+// fused epilogue.  Replaces the three MKL cblas_sgemm call sites of the training
+// step (forward mlp_omp.cc:474-488, weight gradient :565-580, input gradient
+// :655-671) for bf16 (kind::f16) and fp32-as-tf32 (kind::tf32) operands with fp32
+// accumulation.
+//
+// One persistent CTA per SM, 192 threads:
+//   warp 0      TMA producer (one elected lane): fills a ring of shared-memory
+//               stages, each holding a 128 x 128-byte A slab and a BN x 128-byte
+//               B slab in the 128-byte-swizzled layout the MMA descriptors expect
+//   warp 1      allocates TMEM; one elected lane issues tcgen05.mma (M = 128,
+//               N = BN, 32 bytes of K per instruction) into one of two TMEM
+//               accumulators and commits stage / accumulator completion to mbarriers
+//   warps 2-5   epilogue: tcgen05.ld the finished accumulator (each warp its own
+//               32-lane quarter), apply ReLU / ReLU-mask / scaling, convert and
+//               store; runs while the MMA warp works on the next tile
+//
+// Operand layouts.  Row-major storage gives a K-contiguous ("K-major") operand
+// only for the forward GEMM; the input-gradient GEMM reads W with N contiguous
+// and the weight-gradient GEMM reads both operands with M/N contiguous (the
+// contraction runs over batch rows).  Both cases are served without a transpose
+// pass: a K-major slab is one TMA box {128 B of K, rows}; an MN-major slab is a
+// row of boxes {128 B of M/N, BLOCK_K k-rows}, and the shared-memory descriptor's
+// leading/stride byte offsets plus the instruction descriptor's major bits tell
+// the tensor core which one it is looking at.
+//
+// Every wait on an mbarrier is bounded (about two seconds of wall time); a wait
+// that gives up raises an abort flag, the kernel records a code in `status`,
+// releases its TMEM and returns.
+#include <cuda.h>
+
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace b2 {
+namespace {
+
+constexpr int BLOCK_M = 128;
+constexpr int SLAB_BYTES = 128;          // bytes of the contiguous dimension per smem row
+constexpr int KSTEP_BYTES = 32;          // bytes of K one tcgen05.mma consumes
+constexpr int KSTEPS = SLAB_BYTES / KSTEP_BYTES;
+constexpr int MAX_STAGES = 8;
+constexpr int NUM_THREADS = 192;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+
+struct TcParams {
+  int M, N, K;
+  int num_m_blocks, num_n_blocks, num_k_blocks;
+  int block_n, block_k;  // block_k in elements (128 bytes of K)
+  int stages;
+  int tmem_cols;
+  uint32_t idesc;
+  int kind_tf32;
+  int a_mn, b_mn;                  // 1 = operand stored with M/N contiguous
+  uint32_t a_lbo, a_sbo, a_kstep;  // shared-memory descriptor strides / per-k-step advance (bytes)
+  uint32_t b_lbo, b_sbo, b_kstep;
+  uint32_t a_layout, b_layout;     // descriptor swizzle code: 2 = 128 B, 1 = 128 B with 32-byte atoms
+  int a_boxes, b_boxes;            // TMA boxes per stage
+  uint32_t a_box_bytes, b_box_bytes;
+  int a_box_mn, b_box_mn;          // M/N elements covered by one box
+  uint32_t a_stage_bytes, b_stage_bytes;
+  void* C;
+  long long ldc;
+  const void* aux;
+  long long ldaux;
+  int out_bf16, aux_bf16, epilogue;
+  float alpha;
+  unsigned int* status;
+};
+
+// ------------------------------------------------------------------ PTX wrappers
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ unsigned long long globaltimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait. Returns false when it gave up or another role raised the abort flag.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          unsigned int* status, unsigned int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer();
+  unsigned int spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 0xFF) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer() - t0 > WAIT_LIMIT_NS) {
+        *abort_flag = 1;
+        atomicCAS(status, 0u, code);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint64_t* bar, void* dst, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                       uint32_t accumulate, int tf32) {
+  if (tf32) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// 64-bit shared-memory matrix descriptor (version 1) for a 128-byte-swizzled slab.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo, uint32_t layout) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;  // descriptor version (Blackwell)
+  d |= (uint64_t)layout << 61;
+  return d;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// ------------------------------------------------------------------------ kernel
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+               const TcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[MAX_STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[MAX_STAGES];
+  __shared__ __align__(8) uint64_t acc_full_bar[2];
+  __shared__ __align__(8) uint64_t acc_empty_bar[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_s;
+
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t stage_bytes = p.a_stage_bytes + p.b_stage_bytes;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int* abort_flag = &abort_s;
+
+  if (threadIdx.x == 0) {
+    abort_s = 0;
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full_bar[a], 1);
+      mbar_init(&acc_empty_bar[a], 4);  // one arrival per epilogue warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tma_a) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tma_b) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)),
+                 "r"((uint32_t)p.tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+
+  const int num_tiles = p.num_m_blocks * p.num_n_blocks;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m_blk = tile % p.num_m_blocks, n_blk = tile / p.num_m_blocks;
+        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, 1u)) { ok = false; break; }
+          uint8_t* sa = smem + (size_t)stage * stage_bytes;
+          uint8_t* sb = sa + p.a_stage_bytes;
+          mbar_expect_tx(&full_bar[stage], stage_bytes);
+          const int k0 = kb * p.block_k;
+          if (p.a_mn) {
+            for (int b = 0; b < p.a_boxes; ++b)
+              tma_load_2d(&tma_a, &full_bar[stage], sa + (size_t)b * p.a_box_bytes,
+                          m_blk * BLOCK_M + b * p.a_box_mn, k0);
+          } else {
+            tma_load_2d(&tma_a, &full_bar[stage], sa, k0, m_blk * BLOCK_M);
+          }
+          if (p.b_mn) {
+            for (int b = 0; b < p.b_boxes; ++b)
+              tma_load_2d(&tma_b, &full_bar[stage], sb + (size_t)b * p.b_box_bytes,
+                          n_blk * p.block_n + b * p.b_box_mn, k0);
+          } else {
+            tma_load_2d(&tma_b, &full_bar[stage], sb, k0, n_blk * p.block_n);
+          }
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        // give copies already in flight a bounded time to land before the CTA retires
+        const unsigned long long t0 = globaltimer();
+        while (globaltimer() - t0 < 2000000ull) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(&acc_empty_bar[acc], acc_phase ^ 1, abort_flag, p.status, 2u)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * p.block_n);
+        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 3u)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + (size_t)stage * stage_bytes);
+          const uint32_t sb = sa + p.a_stage_bytes;
+#pragma unroll
+          for (int ks = 0; ks < KSTEPS; ++ks) {
+            const uint64_t adesc = make_smem_desc(sa + ks * p.a_kstep, p.a_lbo, p.a_sbo, p.a_layout);
+            const uint64_t bdesc = make_smem_desc(sb + ks * p.b_kstep, p.b_lbo, p.b_sbo, p.b_layout);
+            tc_mma(tmem_d, adesc, bdesc, p.idesc, (uint32_t)((kb | ks) != 0), p.kind_tf32);
+          }
+          tc_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        tc_commit(&acc_full_bar[acc]);   // accumulator complete -> epilogue
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      const int m_blk = tile % p.num_m_blocks, n_blk = tile / p.num_m_blocks;
+      if (!mbar_wait(&acc_full_bar[acc], acc_phase, abort_flag, p.status, 4u)) break;
+      tc_fence_after();
+      const int row = m_blk * BLOCK_M + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      for (int c0 = 0; c0 < p.block_n; c0 += 32) {
+        const int col0 = n_blk * p.block_n + c0;
+        if (col0 >= p.N) break;  // uniform across the warp
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * p.block_n + c0), r);
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+        const bool full = (col0 + 32 <= p.N);
+        if (p.epilogue == EPI_RELU) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
+        } else if (p.epilogue == EPI_MASK && row_ok) {
+          if (p.aux_bf16) {
+            const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(p.aux) + (long long)row * p.ldaux + col0;
+            if (full) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint4 u = __ldg(reinterpret_cast<const uint4*>(x) + j);
+                const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                  // a bf16 is positive iff it is non-zero with the sign bit clear
+                  uint32_t lo = w[t] & 0xFFFFu, hi = w[t] >> 16;
+                  if (!(lo != 0 && lo < 0x8000u)) v[j * 8 + t * 2] = 0.f;
+                  if (!(hi != 0 && hi < 0x8000u)) v[j * 8 + t * 2 + 1] = 0.f;
+                }
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N && !(__bfloat162float(x[j]) > 0.f)) v[j] = 0.f;
+            }
+          } else {
+            const float* x = static_cast<const float*>(p.aux) + (long long)row * p.ldaux + col0;
+            if (full) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                float4 u = __ldg(reinterpret_cast<const float4*>(x) + j);
+                if (!(u.x > 0.f)) v[j * 4 + 0] = 0.f;
+                if (!(u.y > 0.f)) v[j * 4 + 1] = 0.f;
+                if (!(u.z > 0.f)) v[j * 4 + 2] = 0.f;
+                if (!(u.w > 0.f)) v[j * 4 + 3] = 0.f;
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N && !(x[j] > 0.f)) v[j] = 0.f;
+            }
+          }
+        }
+        if (row_ok) {
+          if (p.out_bf16) {
+            __nv_bfloat16* c = static_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
+            if (full) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint4 o;
+                o.x = pack_bf16(v[j * 8 + 0], v[j * 8 + 1]);
+                o.y = pack_bf16(v[j * 8 + 2], v[j * 8 + 3]);
+                o.z = pack_bf16(v[j * 8 + 4], v[j * 8 + 5]);
+                o.w = pack_bf16(v[j * 8 + 6], v[j * 8 + 7]);
+                reinterpret_cast<uint4*>(c)[j] = o;
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) c[j] = __float2bfloat16_rn(v[j]);
+            }
+          } else {
+            float* c = static_cast<float*>(p.C) + (long long)row * p.ldc + col0;
+            if (full) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                reinterpret_cast<float4*>(c)[j] = make_float4(v[j * 4], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) c[j] = v[j];
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)p.tmem_cols)
+                 : "memory");
+  }
+}
+
+// ------------------------------------------------------------------ host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2-D tensor map over a row-major matrix: `inner` contiguous elements per row,
+// `outer` rows, `ld` elements between rows; box = box_inner x box_outer.
+bool make_map(CUtensorMap* map, const void* base, int elem_bytes, long long inner, long long outer, long long ld,
+              int box_inner, int box_outer, bool atom32) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * elem_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  CUresult r = enc(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+struct TcPlan {
+  CUtensorMap map_a, map_b;
+  TcParams p;
+  int grid;
+  size_t smem;
+};
+
+TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t errlen) {
+  auto fail = [&](const char* why) -> TcPlan* {
+    if (err && errlen) snprintf(err, errlen, "%s", why);
+    return nullptr;
+  };
+  const int eb = g.in_type == T_BF16 ? 2 : 4;
+  const int ob = g.out_type == T_BF16 ? 2 : 4;
+  if (g.M <= 0 || g.N <= 0 || g.K <= 0) return fail("empty GEMM");
+  if (g.beta != 0.f) return fail("beta != 0");
+  const bool a_mn = (g.sAm == 1 && g.sAk != 1), b_mn = (g.sBn == 1 && g.sBk != 1);
+  if (!a_mn && g.sAk != 1) return fail("A has no unit stride");
+  if (!b_mn && g.sBk != 1) return fail("B has no unit stride");
+  const long long lda = a_mn ? g.sAk : g.sAm, ldb = b_mn ? g.sBk : g.sBn;
+  auto aligned = [](const void* p, long long ld, int bytes) {
+    return (reinterpret_cast<uintptr_t>(p) % 16 == 0) && ((ld * bytes) % 16 == 0);
+  };
+  if (!aligned(g.A, lda, eb) || !aligned(g.B, ldb, eb)) return fail("operand not 16-byte aligned");
+  if (!aligned(g.C, g.ldc, ob)) return fail("output not 16-byte aligned");
+  if (g.epilogue == EPI_MASK && !aligned(g.aux, g.ldaux, eb)) return fail("mask operand not 16-byte aligned");
+  if (g.N < 16) return fail("N < 16");
+
+  TcPlan* plan = new TcPlan();
+  TcParams& p = plan->p;
+  memset(&p, 0, sizeof p);
+  p.M = g.M; p.N = g.N; p.K = g.K;
+  p.block_k = SLAB_BYTES / eb;
+  // Tile width: the widest of 256/128/64 that still gives every SM a tile.
+  int bn = 256;
+  auto tiles = [&](int n) { return (long long)((g.M + BLOCK_M - 1) / BLOCK_M) * ((g.N + n - 1) / n); };
+  while (bn > 64 && (tiles(bn) < sm_count || bn / 2 >= g.N)) bn /= 2;
+  p.block_n = bn;
+  p.num_m_blocks = (g.M + BLOCK_M - 1) / BLOCK_M;
+  p.num_n_blocks = (g.N + bn - 1) / bn;
+  p.num_k_blocks = (g.K + p.block_k - 1) / p.block_k;
+  p.tmem_cols = 2 * bn < 32 ? 32 : 2 * bn;  // 128, 256 or 512: powers of two
+  p.kind_tf32 = (eb == 4);
+  p.a_mn = a_mn; p.b_mn = b_mn;
+  const uint32_t fmt = (eb == 4) ? 2u : 1u;  // tf32 : bf16
+  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) |
+            ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BLOCK_M >> 4) << 24);
+  const int slab_elems = SLAB_BYTES / eb;
+  p.a_stage_bytes = BLOCK_M * SLAB_BYTES;
+  p.b_stage_bytes = bn * SLAB_BYTES;
+  bool ok = true;
+  // M/N-contiguous operands: 16-bit elements use the plain 128-byte swizzle (8 k-rows of
+  // 128 B per 1024-byte group); 32-bit elements are only accepted in the variant that
+  // swizzles 32-byte atoms (4 k-rows per 512-byte group).
+  const bool mn_atom32 = (eb == 4);
+  const uint32_t mn_group_bytes = mn_atom32 ? 512 : 1024;
+  const uint32_t mn_layout = mn_atom32 ? 1 : 2;
+  if (a_mn) {
+    // boxes of {128 bytes of M, block_k k-rows}; 8-row groups 1024 B apart, M atoms one box apart
+    p.a_boxes = BLOCK_M / slab_elems;
+    p.a_box_mn = slab_elems;
+    p.a_box_bytes = p.block_k * SLAB_BYTES;
+    p.a_lbo = p.a_box_bytes;
+    p.a_sbo = mn_group_bytes;
+    p.a_layout = mn_layout;
+    p.a_kstep = (KSTEP_BYTES / eb) * SLAB_BYTES;
+    ok = ok && make_map(&plan->map_a, g.A, eb, g.M, g.K, lda, slab_elems, p.block_k, mn_atom32);
+  } else {
+    p.a_boxes = 1;
+    p.a_box_bytes = p.a_stage_bytes;
+    p.a_lbo = 16;
+    p.a_sbo = 1024;
+    p.a_kstep = KSTEP_BYTES;
+    p.a_layout = 2;
+    ok = ok && make_map(&plan->map_a, g.A, eb, g.K, g.M, lda, p.block_k, BLOCK_M, false);
+  }
+  if (b_mn) {
+    p.b_boxes = bn / slab_elems;
+    p.b_box_mn = slab_elems;
+    p.b_box_bytes = p.block_k * SLAB_BYTES;
+    p.b_lbo = p.b_box_bytes;
+    p.b_sbo = mn_group_bytes;
+    p.b_layout = mn_layout;
+    p.b_kstep = (KSTEP_BYTES / eb) * SLAB_BYTES;
+    ok = ok && make_map(&plan->map_b, g.B, eb, g.N, g.K, ldb, slab_elems, p.block_k, mn_atom32);
+  } else {
+    p.b_boxes = 1;
+    p.b_box_bytes = p.b_stage_bytes;
+    p.b_lbo = 16;
+    p.b_sbo = 1024;
+    p.b_kstep = KSTEP_BYTES;
+    p.b_layout = 2;
+    ok = ok && make_map(&plan->map_b, g.B, eb, g.K, g.N, ldb, p.block_k, bn, false);
+  }
+  if (!ok) {
+    delete plan;
+    return fail("cuTensorMapEncodeTiled failed");
+  }
+  const size_t stage = p.a_stage_bytes + p.b_stage_bytes;
+  int stages = (int)((200 * 1024) / stage);
+  if (stages > MAX_STAGES) stages = MAX_STAGES;
+  p.stages = stages;
+  // Always ask for the same large carve-out so that only one CTA (one TMEM
+  // allocation) is ever resident per SM.
+  plan->smem = 1024 + (size_t)stages * stage;
+  if (plan->smem < 140 * 1024) plan->smem = 140 * 1024;
+  p.C = g.C; p.ldc = g.ldc; p.aux = g.aux; p.ldaux = g.ldaux;
+  p.out_bf16 = g.out_type == T_BF16;
+  p.aux_bf16 = g.in_type == T_BF16;
+  p.epilogue = g.epilogue;
+  p.alpha = g.alpha;
+  const long long nt = (long long)p.num_m_blocks * p.num_n_blocks;
+  plan->grid = (int)(nt < sm_count ? nt : sm_count);
+  return plan;
+}
+
+void gemm_tc_plan_destroy(TcPlan* p) { delete p; }
+
+cudaError_t gemm_tc_launch(const TcPlan* plan, cudaStream_t stream, unsigned int* status) {
+  static unsigned long long attr_set = 0;  // one bit per device ordinal
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!(attr_set >> (dev & 63) & 1ull)) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
+    if (e != cudaSuccess) return e;
+    attr_set |= 1ull << (dev & 63);
+  }
+  TcParams p = plan->p;
+  p.status = status;
+  gemm_tc_kernel<<<plan->grid, NUM_THREADS, plan->smem, stream>>>(plan->map_a, plan->map_b, p);
+  return cudaGetLastError();
+}
+
+}  // namespace b2

@@ -1,0 +1,82 @@
+// Run-time binding of the few NCCL entry points the gradient allreduce needs.
+// The library is looked up when the first multi-GPU handle is created, so a
+// single-GPU job has no NCCL dependency, and a process that already loaded NCCL
+// (for instance through PyTorch) shares that copy instead of loading a second one.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+#include <glob.h>
+#include <stddef.h>
+
+#include <mutex>
+#include <string>
+
+namespace b2 {
+
+// ABI-stable subset of nccl.h (NCCL 2.x).
+typedef struct ncclComm* ncclComm_t;
+typedef struct { char internal[128]; } ncclUniqueId;
+enum { ncclSuccess = 0, ncclInProgress = 7 };
+enum { ncclFloat32 = 7, ncclBfloat16 = 9 };
+enum { ncclSum = 0 };
+
+struct NcclApi {
+  int (*GetUniqueId)(ncclUniqueId*) = nullptr;
+  int (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+  int (*CommDestroy)(ncclComm_t) = nullptr;
+  int (*CommAbort)(ncclComm_t) = nullptr;
+  int (*AllReduce)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+  int (*CommGetAsyncError)(ncclComm_t, int*) = nullptr;
+  const char* (*GetErrorString)(int) = nullptr;
+  int (*GetVersion)(int*) = nullptr;
+  std::string path, error;
+  bool ok = false;
+};
+
+inline NcclApi& nccl_api() {
+  static NcclApi api;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* h = nullptr;
+    const char* env = getenv("B2_NCCL_PATH");
+    if (env) h = dlopen(env, RTLD_NOW | RTLD_GLOBAL);
+    if (h) api.path = env;
+    if (!h) {
+      // already mapped by the hosting process?
+      h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD | RTLD_GLOBAL);
+      if (h) api.path = "libnccl.so.2 (already loaded)";
+    }
+    const char* pats[] = {"/opt/*/.venv/lib/python3*/site-packages/nvidia/nccl/lib/libnccl.so.2",
+                          "/usr/lib/x86_64-linux-gnu/libnccl.so.2", "/usr/local/cuda/lib64/libnccl.so.2"};
+    for (size_t i = 0; i < sizeof(pats) / sizeof(pats[0]) && !h; ++i) {
+      glob_t g;
+      if (glob(pats[i], 0, nullptr, &g) == 0) {
+        for (size_t j = 0; j < g.gl_pathc && !h; ++j) {
+          h = dlopen(g.gl_pathv[j], RTLD_NOW | RTLD_GLOBAL);
+          if (h) api.path = g.gl_pathv[j];
+        }
+      }
+      globfree(&g);
+    }
+    if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) {
+      api.error = "libnccl.so.2 not found (set B2_NCCL_PATH)";
+      return;
+    }
+    auto sym = [&](const char* n) { return dlsym(h, n); };
+    api.GetUniqueId = (decltype(api.GetUniqueId))sym("ncclGetUniqueId");
+    api.CommInitRank = (decltype(api.CommInitRank))sym("ncclCommInitRank");
+    api.CommDestroy = (decltype(api.CommDestroy))sym("ncclCommDestroy");
+    api.CommAbort = (decltype(api.CommAbort))sym("ncclCommAbort");
+    api.AllReduce = (decltype(api.AllReduce))sym("ncclAllReduce");
+    api.CommGetAsyncError = (decltype(api.CommGetAsyncError))sym("ncclCommGetAsyncError");
+    api.GetErrorString = (decltype(api.GetErrorString))sym("ncclGetErrorString");
+    api.GetVersion = (decltype(api.GetVersion))sym("ncclGetVersion");
+    api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllReduce && api.GetErrorString;
+    if (!api.ok) api.error = "libnccl.so.2 lacks a required symbol";
+  });
+  return api;
+}
+
+}  // namespace b2

@@ -1,0 +1,89 @@
+// C exports of the host-side mirror (Partition, TwistedHyperCube, ring tables,
+// Matrix layout, seeded fills) so that the test-suite can compare them, through
+// ctypes, with golden vectors produced by the reference's own functions.
+#include <cstring>
+
+#include "TwistedHyperCube.h"
+#include "mlp_bench_common.h"
+
+extern "C" {
+
+void b2h_get_partition(int nsock, int work, int socket_id, int nthr, int tid, int* out2) {
+  nsockets = nsock;
+  auto p = get_partition(work, socket_id, nthr, tid);
+  out2[0] = p.first;
+  out2[1] = p.second;
+}
+
+int b2h_work_per_socket(int nsock, int work) {
+  nsockets = nsock;
+  return get_work_per_socket(work);
+}
+
+void b2h_intra_socket_2d(int m, int n, double ar, int m_align, int nthr, int tid, int* out4) {
+  get_intra_socket_2dpartition(&out4[0], &out4[1], &out4[2], &out4[3], m, n, ar, m_align != 0, nthr, tid);
+}
+
+void b2h_2dpartition(int nsock, int m, int n, double ar, int m_align, int socket_id, int nthr, int tid, int* out4) {
+  nsockets = nsock;
+  get_2dpartition(&out4[0], &out4[1], &out4[2], &out4[3], m, n, ar, m_align != 0, socket_id, nthr, tid);
+}
+
+void b2h_hypercube(int twisted, int num_nodes, int shift, int id, int dim, int* out3) {
+  if (twisted) {
+    TwistedHyperCube c(num_nodes, shift);
+    out3[0] = c.Peer(id, dim);
+    out3[1] = c.RecvLocation(id, dim);
+    out3[2] = c.SendLocation(id, dim);
+  } else {
+    HyperCube c(num_nodes, shift);
+    out3[0] = c.Peer(id, dim);
+    out3[1] = c.RecvLocation(id, dim);
+    out3[2] = c.SendLocation(id, dim);
+  }
+}
+
+void b2h_ring_info(int nsock, int sid, int task, int* out3) {
+  nsockets = nsock;
+  get_my_ring_info(sid, task, &out3[0], &out3[1], &out3[2]);
+}
+
+// Matrix<float, 16> layout facts: ld, allocation alignment, element addressing.
+void b2h_matrix_layout(int rows, int cols, int* ld, int* aligned4k, long long* offset_last) {
+  Matrix<float, PAD> m(rows, cols);
+  *ld = m.ld();
+  *aligned4k = (reinterpret_cast<uintptr_t>(m.rawData()) % 4096) == 0;
+  *offset_last = m.rawData(rows - 1, cols - 1) - m.rawData();
+}
+
+// init_matrices() on a fresh model; returns the input and the weights densely.
+void b2h_init_matrices(int nlayers_, const int* widths, int batch, int nsock, float* x, float** w) {
+  nsockets = nsock;
+  set_model(std::vector<int>(widths, widths + nlayers_ + 1));
+  activations[0].reset(new Matrix<float, PAD>(batch, nfeatures[0]));
+  for (int l = 0; l < nlayers; ++l)
+    weights[l].reset(new Matrix<float, PAD>(nsock * nfeatures[l + 1], nfeatures[l]));
+  randSeed(3);
+  init_matrices();
+  for (int i = 0; i < batch; ++i) memcpy(x + (size_t)i * nfeatures[0], activations[0]->rawData(i, 0), 4 * nfeatures[0]);
+  for (int l = 0; l < nlayers; ++l)
+    for (int i = 0; i < nsock * nfeatures[l + 1]; ++i)
+      memcpy(w[l] + (size_t)i * nfeatures[l], weights[l]->rawData(i, 0), 4 * nfeatures[l]);
+}
+
+// print_checksum arithmetic on a dense matrix: l1, l2, trace.
+void b2h_checksum(const float* w, int rows, int cols, double* out3) {
+  double l1 = 0, l2 = 0, tr = 0;
+  for (int i = 0; i < rows; ++i) {
+    for (int j = 0; j < cols; ++j) {
+      float v = w[(size_t)i * cols + j];
+      l1 += std::abs(v);
+      l2 += v * v;
+    }
+    if (i < std::min(rows, cols)) tr += w[(size_t)i * cols + i];
+  }
+  out3[0] = l1;
+  out3[1] = std::sqrt(l2);
+  out3[2] = tr;
+}
+}
