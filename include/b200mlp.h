@@ -144,6 +144,17 @@ int b2_step(b2_handle* h, int iters);
  * (b2_host_alloc) makes the copies asynchronous. */
 int b2_train_step_host(b2_handle* h, const float* x, size_t ldx, const float* t, size_t ldt,
                        double* loss);
+/* Pipelined form of the same call for input streams: enqueues the copy of this
+ * step's inputs (on a copy stream, into one of two input slots) and the step, and
+ * returns without waiting, so that the copy of step i+1 overlaps the compute of
+ * step i. At most two steps may be in flight; b2_wait_loss() blocks until the
+ * oldest one has finished and returns its loss share. `x` and `t` must stay valid
+ * and unchanged until that step's b2_wait_loss() returns, and should be pinned.
+ * Needs collect_timing = 0 and use_graph = 0. The reference has no counterpart
+ * (its inputs never change, mlp_bench_common.cc:18); this is the form a data-loader
+ * driven caller of the training step uses. */
+int b2_train_step_host_async(b2_handle* h, const float* x, size_t ldx, const float* t, size_t ldt);
+int b2_wait_loss(b2_handle* h, double* loss);
 /* Loss of the most recent step (this rank's share). */
 int b2_loss(b2_handle* h, double* loss);
 

@@ -54,6 +54,8 @@ SYMBOLS = {
     "b2_set_lr": (C.c_int, [_H, C.c_float]),
     "b2_step": (C.c_int, [_H, C.c_int]),
     "b2_train_step_host": (C.c_int, [_H, _fp, C.c_size_t, _fp, C.c_size_t, _dp]),
+    "b2_train_step_host_async": (C.c_int, [_H, _fp, C.c_size_t, _fp, C.c_size_t]),
+    "b2_wait_loss": (C.c_int, [_H, _dp]),
     "b2_loss": (C.c_int, [_H, _dp]),
     "b2_host_alloc": (C.c_int, [C.POINTER(C.c_void_p), C.c_size_t]),
     "b2_host_free": (C.c_int, [C.c_void_p]),
@@ -76,12 +78,15 @@ def lib():
     """The loaded shared library with argument types set; raises if it is missing."""
     global _lib
     if _lib is None:
-        if not os.path.exists(LIB_PATH):
+        path = os.environ.get("B2_LIB_PATH", LIB_PATH)  # override: A/B runs of two builds
+        if not os.path.exists(path):
             raise ImportError(
-                f"{LIB_PATH} is missing: build it with `python -m tbb_test_b200.build` "
+                f"{path} is missing: build it with `python -m tbb_test_b200.build` "
                 "(there is no CPU or PyTorch fallback)")
-        L = C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL)
+        L = C.CDLL(path, mode=C.RTLD_GLOBAL)
         for name, (res, args) in SYMBOLS.items():
+            if path != LIB_PATH and not hasattr(L, name):
+                continue
             fn = getattr(L, name)
             fn.restype = res
             fn.argtypes = args

@@ -55,7 +55,7 @@ struct b2_handle {
   void* dinput = nullptr;
   float* stage = nullptr;  // fp32 staging for converted up/downloads
   size_t stage_elems = 0;
-  double* loss_dev = nullptr;
+  double* loss_dev = nullptr;  // [2]: one accumulator per input slot
   unsigned int* status_dev = nullptr;
   std::vector<cudaEvent_t> ev_wgrad, ev_dgrad, ev_upd;
   std::vector<char> upd_pending;
@@ -63,6 +63,18 @@ struct b2_handle {
   std::vector<cudaEvent_t> ev_phase;  // [iters][L][B2_T_NUM][2], alive during one b2_step call
   int ev_iter = 0;                    // step of the current call the recorder is in
   std::vector<Site> fwd, wgrad, dgrad;
+  // second input slot of the pipelined host-fed path (b2_train_step_host_async): while a
+  // step computes on slot 0 the next step's inputs are copied into slot 1 and vice versa
+  void* act0_alt = nullptr;
+  float* target_alt = nullptr;
+  float* xstage[2] = {nullptr, nullptr};  // fp32 landing buffers when the operands are bf16
+  Site fwd0_alt, wgrad0_alt;
+  cudaStream_t s_copy = nullptr;
+  cudaEvent_t ev_copied[2] = {nullptr, nullptr}, ev_slot_free[2] = {nullptr, nullptr},
+              ev_loss[2] = {nullptr, nullptr};
+  bool slot_used[2] = {false, false};
+  double* loss_host = nullptr;  // pinned, one value per slot
+  long long async_issued = 0, async_waited = 0;
   ncclComm_t comm = nullptr;
   std::vector<double> phase_ms;
   double step_ms = 0;
@@ -229,6 +241,14 @@ int build_sites(b2_handle* h) {
     h->dgrad[l].d = b;
     make_site(h, h->dgrad[l], tc);
     if (l == 0 && !h->cfg.input_grad) h->dgrad[l].active = false;
+    if (l == 0) {  // layer 0 reads the network input: one more pair of sites for the second slot
+      h->fwd0_alt.d = f;
+      h->fwd0_alt.d.A = h->act0_alt;
+      make_site(h, h->fwd0_alt, tc);
+      h->wgrad0_alt.d = g;
+      h->wgrad0_alt.d.B = h->act0_alt;
+      make_site(h, h->wgrad0_alt, tc);
+    }
   }
   return B2_OK;
 }
@@ -255,33 +275,34 @@ int layer_sgd(b2_handle* h, int l, cudaStream_t st, bool timed) {
 }
 
 // Enqueue one training step on the two streams (no host synchronisation).
-int enqueue_step(b2_handle* h, bool timed) {
+int enqueue_step(b2_handle* h, bool timed, int slot = 0) {
   const int L = h->L;
+  double* loss_acc = h->loss_dev + slot;
+  const float* target = slot ? h->target_alt : h->target;
   const bool overlap = h->cfg.overlap != 0;
   cudaStream_t sm = h->s_main, sc = overlap ? h->s_comm : h->s_main;
   int rc;
-  CK(h, cudaMemsetAsync(h->loss_dev, 0, sizeof(double), sm));
+  CK(h, cudaMemsetAsync(loss_acc, 0, sizeof(double), sm));
   for (int l = 0; l < L; ++l) {
     if (overlap && h->upd_pending[l]) {
       CK(h, cudaStreamWaitEvent(sm, h->ev_upd[l], 0));
       h->upd_pending[l] = 0;
     }
     if (timed) CK(h, cudaEventRecord(phase_ev(h, l, B2_T_FWD, 0), sm));
-    if ((rc = run_site(h, h->fwd[l], sm))) return rc;
+    if ((rc = run_site(h, (l == 0 && slot) ? h->fwd0_alt : h->fwd[l], sm))) return rc;
     if (timed) CK(h, cudaEventRecord(phase_ev(h, l, B2_T_FWD, 1), sm));
   }
   {
     const size_t n = (size_t)h->bl * h->nf[L];
     const bool baseline = h->cfg.mode == B2_MODE_BASELINE;
-    CK(h, loss_grad_launch(h->y, h->target, h->dz[L - 1], h->op_type, n, baseline ? 1 : 0,
-                           1.0f / (float)h->cfg.batch, baseline ? 1.0 / (double)h->cfg.batch : 1.0, h->loss_dev,
-                           sm));
+    CK(h, loss_grad_launch(h->y, target, h->dz[L - 1], h->op_type, n, baseline ? 1 : 0,
+                           1.0f / (float)h->cfg.batch, baseline ? 1.0 / (double)h->cfg.batch : 1.0, loss_acc, sm));
     if (n) ++h->launches;
   }
   for (int l = L - 1; l >= 0; --l) {
     if (timed) CK(h, cudaEventRecord(phase_ev(h, l, B2_T_WGT_GRAD, 0), sm));
     if (h->wgrad[l].active) {
-      if ((rc = run_site(h, h->wgrad[l], sm))) return rc;
+      if ((rc = run_site(h, (l == 0 && slot) ? h->wgrad0_alt : h->wgrad[l], sm))) return rc;
     } else {  // a rank without batch rows contributes a zero gradient
       CK(h, cudaMemsetAsync(h->dw[l], 0, (size_t)h->nf[l + 1] * h->nf[l] * esize(h->grad_type), sm));
     }
@@ -321,6 +342,7 @@ void free_all(b2_handle* h) {
   cudaSetDevice(h->cfg.device);
   if (h->s_main) cudaStreamSynchronize(h->s_main);
   if (h->s_comm) cudaStreamSynchronize(h->s_comm);
+  if (h->s_copy) cudaStreamSynchronize(h->s_copy);
   if (h->comm && nccl_api().ok) nccl_api().CommDestroy(h->comm);
   if (h->graph_exec) cudaGraphExecDestroy(h->graph_exec);
   for (auto& s : h->fwd) gemm_tc_plan_destroy(s.plan);
@@ -336,6 +358,19 @@ void free_all(b2_handle* h) {
   cudaFree(h->dinput);
   cudaFree(h->stage);
   cudaFree(h->loss_dev);
+  cudaFree(h->act0_alt);
+  cudaFree(h->target_alt);
+  cudaFree(h->xstage[0]);
+  cudaFree(h->xstage[1]);
+  if (h->loss_host) cudaFreeHost(h->loss_host);
+  gemm_tc_plan_destroy(h->fwd0_alt.plan);
+  gemm_tc_plan_destroy(h->wgrad0_alt.plan);
+  for (int i = 0; i < 2; ++i) {
+    if (h->ev_copied[i]) cudaEventDestroy(h->ev_copied[i]);
+    if (h->ev_slot_free[i]) cudaEventDestroy(h->ev_slot_free[i]);
+    if (h->ev_loss[i]) cudaEventDestroy(h->ev_loss[i]);
+  }
+  if (h->s_copy) cudaStreamDestroy(h->s_copy);
   cudaFree(h->status_dev);
   for (auto e : h->ev_wgrad) cudaEventDestroy(e);
   for (auto e : h->ev_dgrad) cudaEventDestroy(e);
@@ -482,7 +517,18 @@ int b2_create(const b2_config* cfg, b2_handle** out) {
     h->stage_elems = max_elems;
     TRY(dev_alloc(h, &h->stage, max_elems * 4));
   }
-  TRY(dev_alloc(h, &h->loss_dev, sizeof(double)));
+  TRY(dev_alloc(h, &h->act0_alt, bl * h->nf[0] * esize(h->op_type)));
+  TRY(dev_alloc(h, &h->target_alt, bl * h->nf[L] * 4));
+  if (h->op_type == T_BF16)
+    for (int i = 0; i < 2; ++i) TRY(dev_alloc(h, &h->xstage[i], bl * h->nf[0] * 4));
+  TRY(dev_alloc(h, &h->loss_dev, 2 * sizeof(double)));
+  TRYCK(cudaHostAlloc((void**)&h->loss_host, 2 * sizeof(double), cudaHostAllocDefault));
+  TRYCK(cudaStreamCreateWithFlags(&h->s_copy, cudaStreamNonBlocking));
+  for (int i = 0; i < 2; ++i) {
+    TRYCK(cudaEventCreateWithFlags(&h->ev_copied[i], cudaEventDisableTiming));
+    TRYCK(cudaEventCreateWithFlags(&h->ev_slot_free[i], cudaEventDisableTiming));
+    TRYCK(cudaEventCreateWithFlags(&h->ev_loss[i], cudaEventDisableTiming));
+  }
   TRY(dev_alloc(h, &h->status_dev, sizeof(unsigned int)));
 
   h->ev_wgrad.assign(L, nullptr);
@@ -674,6 +720,7 @@ static long long launches_per_step(const b2_handle* h, long long* tc) {
 int b2_step(b2_handle* h, int iters) {
   ENTER(h);
   if (iters < 0) return fail(h, B2_ERR_INVALID, "iters < 0");
+  if (h->async_issued != h->async_waited) return fail(h, B2_ERR_STATE, "pipelined steps in flight: b2_wait_loss first");
   if (iters == 0) return B2_OK;
   const bool timed = h->cfg.collect_timing != 0;
   const bool graph = h->cfg.use_graph && !timed;
@@ -747,6 +794,61 @@ int b2_train_step_host(b2_handle* h, const float* x, size_t ldx, const float* t,
   }
   if ((rc = b2_step(h, 1))) return rc;
   if (loss) return b2_loss(h, loss);
+  return B2_OK;
+}
+
+int b2_train_step_host_async(b2_handle* h, const float* x, size_t ldx, const float* t, size_t ldt) {
+  ENTER(h);
+  if (!x || ldx < (size_t)h->nf[0]) return fail(h, B2_ERR_INVALID, "bad input matrix");
+  if (t && ldt < (size_t)h->nf[h->L]) return fail(h, B2_ERR_INVALID, "bad target matrix");
+  if (h->cfg.collect_timing || h->cfg.use_graph)
+    return fail(h, B2_ERR_STATE, "the pipelined host-fed step needs collect_timing = 0 and use_graph = 0");
+  if (h->async_issued - h->async_waited >= 2)
+    return fail(h, B2_ERR_STATE, "two steps already in flight: call b2_wait_loss first");
+  const int slot = (int)(h->async_issued & 1);
+  const int rows = h->bl, f0 = h->nf[0], fl = h->nf[h->L];
+  int rc;
+  // the copy may start once the step that last computed on this slot is done with it
+  if (h->slot_used[slot]) CK(h, cudaStreamWaitEvent(h->s_copy, h->ev_slot_free[slot], 0));
+  if (rows > 0) {
+    void* act0 = slot ? h->act0_alt : h->act[0];
+    void* land = h->op_type == T_BF16 ? (void*)h->xstage[slot] : act0;
+    CK(h, cudaMemcpy2DAsync(land, (size_t)f0 * 4, x + (size_t)h->b0 * ldx, ldx * 4, (size_t)f0 * 4, rows,
+                            cudaMemcpyHostToDevice, h->s_copy));
+    if (h->op_type == T_BF16) {
+      CK(h, convert_f32_to_bf16(h->xstage[slot], (__nv_bfloat16*)act0, (size_t)rows * f0, h->s_copy));
+      ++h->launches;
+    }
+    if (t)
+      CK(h, cudaMemcpy2DAsync(slot ? h->target_alt : h->target, (size_t)fl * 4, t + (size_t)h->b0 * ldt, ldt * 4,
+                              (size_t)fl * 4, rows, cudaMemcpyHostToDevice, h->s_copy));
+  }
+  CK(h, cudaEventRecord(h->ev_copied[slot], h->s_copy));
+  CK(h, cudaStreamWaitEvent(h->s_main, h->ev_copied[slot], 0));
+  if ((rc = enqueue_step(h, false, slot))) return rc;
+  CK(h, cudaEventRecord(h->ev_slot_free[slot], h->s_main));
+  h->slot_used[slot] = true;
+  CK(h, cudaMemcpyAsync(h->loss_host + slot, h->loss_dev + slot, sizeof(double), cudaMemcpyDeviceToHost,
+                        h->s_main));
+  CK(h, cudaEventRecord(h->ev_loss[slot], h->s_main));
+  ++h->async_issued;
+  ++h->steps;
+  return B2_OK;
+}
+
+int b2_wait_loss(b2_handle* h, double* loss) {
+  ENTER(h);
+  if (h->async_waited >= h->async_issued) return fail(h, B2_ERR_STATE, "no step in flight");
+  const int slot = (int)(h->async_waited & 1);
+  CK(h, cudaEventSynchronize(h->ev_loss[slot]));
+  if (loss) *loss = h->loss_host[slot];
+  ++h->async_waited;
+  if (h->async_waited == h->async_issued) {  // pipeline drained: also let the updates finish
+    int rc = join_streams(h);
+    if (rc) return rc;
+    CK(h, cudaStreamSynchronize(h->s_main));
+    return check_status(h);
+  }
   return B2_OK;
 }
 

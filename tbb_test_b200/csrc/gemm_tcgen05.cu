@@ -30,6 +30,7 @@
 #include <cuda.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -47,8 +48,12 @@ constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
 struct TcParams {
   int M, N, K;
-  int num_m_blocks, num_n_blocks, num_k_blocks;
+  int num_m_blocks, num_n_blocks, num_k_blocks;  // m blocks count super-tiles of sub_m * 128 rows
   int block_n, block_k;  // block_k in elements (128 bytes of K)
+  int sub_m;             // 128-row accumulators per tile: 1 (two TMEM stages) or 2 (one stage)
+  int acc_stages;
+  int num_items;         // work items: whole tiles, then the last partial wave cut in 128-row halves
+  int split_from;        // first tile that is cut in halves
   int stages;
   int tmem_cols;
   uint32_t idesc;
@@ -177,11 +182,41 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Work item -> (first row, number of 128-row sub-blocks, column block). Tiles are
+// numbered with the row block fastest; tiles from p.split_from on are handed out as
+// two 128-row halves so that the last, partial wave of a persistent grid costs half
+// a tile time instead of a whole one.
+struct Item {
+  int m0, sub, n_blk;
+};
+template <int SUB_M>
+__device__ __forceinline__ Item decode_item(int w, int split_from, int num_m_blocks, int M) {
+  int tile = w, half = -1;
+  if (SUB_M == 2 && w >= split_from) {
+    tile = split_from + ((w - split_from) >> 1);
+    half = (w - split_from) & 1;
+  }
+  Item it;
+  it.n_blk = tile / num_m_blocks;
+  it.m0 = (tile % num_m_blocks) * (SUB_M * BLOCK_M);
+  it.sub = SUB_M;
+  if (SUB_M == 2) {
+    if (half >= 0) {
+      it.m0 += half * BLOCK_M;
+      it.sub = 1;
+    } else if (it.m0 + BLOCK_M >= M) {
+      it.sub = 1;  // ragged last row block: the second half would be empty
+    }
+  }
+  return it;
+}
+
 // ------------------------------------------------------------------------ kernel
 
+template <int SUB_M>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-               const TcParams p) {
+               const __grid_constant__ TcParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[MAX_STAGES];
   __shared__ __align__(8) uint64_t empty_bar[MAX_STAGES];
@@ -220,7 +255,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_s;
 
-  const int num_tiles = p.num_m_blocks * p.num_n_blocks;
+  const int num_items = p.num_items;
+  const uint32_t acc_cols = (uint32_t)(SUB_M * p.block_n);  // TMEM columns of one accumulator stage
+  constexpr int ACC_STAGES = SUB_M == 2 ? 1 : 2;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -228,27 +265,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m_blk = tile % p.num_m_blocks, n_blk = tile / p.num_m_blocks;
+      for (int w = blockIdx.x; w < num_items && ok; w += gridDim.x) {
+        const Item it = decode_item<SUB_M>(w, p.split_from, p.num_m_blocks, p.M);
+        const uint32_t a_bytes = (uint32_t)it.sub * (BLOCK_M * SLAB_BYTES);
         for (int kb = 0; kb < p.num_k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, 1u)) { ok = false; break; }
           uint8_t* sa = smem + (size_t)stage * stage_bytes;
           uint8_t* sb = sa + p.a_stage_bytes;
-          mbar_expect_tx(&full_bar[stage], stage_bytes);
+          mbar_expect_tx(&full_bar[stage], a_bytes + p.b_stage_bytes);
           const int k0 = kb * p.block_k;
           if (p.a_mn) {
-            for (int b = 0; b < p.a_boxes; ++b)
-              tma_load_2d(&tma_a, &full_bar[stage], sa + (size_t)b * p.a_box_bytes,
-                          m_blk * BLOCK_M + b * p.a_box_mn, k0);
+            const int nbox = it.sub * p.a_boxes;  // a_boxes per 128 rows
+            for (int b = 0; b < nbox; ++b)
+              tma_load_2d(&tma_a, &full_bar[stage], sa + (size_t)b * p.a_box_bytes, it.m0 + b * p.a_box_mn, k0);
           } else {
-            tma_load_2d(&tma_a, &full_bar[stage], sa, k0, m_blk * BLOCK_M);
+#pragma unroll
+            for (int i = 0; i < SUB_M; ++i)
+              if (i < it.sub)
+                tma_load_2d(&tma_a, &full_bar[stage], sa + (size_t)i * (BLOCK_M * SLAB_BYTES), k0,
+                            it.m0 + i * BLOCK_M);
           }
           if (p.b_mn) {
             for (int b = 0; b < p.b_boxes; ++b)
               tma_load_2d(&tma_b, &full_bar[stage], sb + (size_t)b * p.b_box_bytes,
-                          n_blk * p.block_n + b * p.b_box_mn, k0);
+                          it.n_blk * p.block_n + b * p.b_box_mn, k0);
           } else {
-            tma_load_2d(&tma_b, &full_bar[stage], sb, k0, n_blk * p.block_n);
+            tma_load_2d(&tma_b, &full_bar[stage], sb, k0, it.n_blk * p.block_n);
           }
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
@@ -267,10 +309,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int w = blockIdx.x; w < num_items && ok; w += gridDim.x) {
+        const Item it = decode_item<SUB_M>(w, p.split_from, p.num_m_blocks, p.M);
         if (!mbar_wait(&acc_empty_bar[acc], acc_phase ^ 1, abort_flag, p.status, 2u)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * p.block_n);
+        const uint32_t tmem_d = tmem_base + (uint32_t)acc * acc_cols;
         for (int kb = 0; kb < p.num_k_blocks; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 3u)) { ok = false; break; }
           tc_fence_after();
@@ -278,17 +321,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           const uint32_t sb = sa + p.a_stage_bytes;
 #pragma unroll
           for (int ks = 0; ks < KSTEPS; ++ks) {
-            const uint64_t adesc = make_smem_desc(sa + ks * p.a_kstep, p.a_lbo, p.a_sbo, p.a_layout);
             const uint64_t bdesc = make_smem_desc(sb + ks * p.b_kstep, p.b_lbo, p.b_sbo, p.b_layout);
-            tc_mma(tmem_d, adesc, bdesc, p.idesc, (uint32_t)((kb | ks) != 0), p.kind_tf32);
+#pragma unroll
+            for (int i = 0; i < SUB_M; ++i) {  // the 128-row sub-blocks share the B slab
+              if (i < it.sub) {
+                const uint64_t adesc = make_smem_desc(sa + i * (BLOCK_M * SLAB_BYTES) + ks * p.a_kstep, p.a_lbo,
+                                                      p.a_sbo, p.a_layout);
+                tc_mma(tmem_d + (uint32_t)(i * p.block_n), adesc, bdesc, p.idesc, (uint32_t)((kb | ks) != 0),
+                       p.kind_tf32);
+              }
+            }
           }
           tc_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
         tc_commit(&acc_full_bar[acc]);   // accumulator complete -> epilogue
-        acc ^= 1;
-        if (acc == 0) acc_phase ^= 1;
+        if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
       }
     }
   } else {
@@ -296,17 +345,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-      const int m_blk = tile % p.num_m_blocks, n_blk = tile / p.num_m_blocks;
+    for (int w = blockIdx.x; w < num_items; w += gridDim.x) {
+      const Item it = decode_item<SUB_M>(w, p.split_from, p.num_m_blocks, p.M);
+      const int n_blk = it.n_blk;
       if (!mbar_wait(&acc_full_bar[acc], acc_phase, abort_flag, p.status, 4u)) break;
       tc_fence_after();
-      const int row = m_blk * BLOCK_M + q * 32 + lane;
+#pragma unroll 1
+      for (int sub = 0; sub < it.sub; ++sub) {
+      const int row = it.m0 + sub * BLOCK_M + q * 32 + lane;
       const bool row_ok = row < p.M;
       for (int c0 = 0; c0 < p.block_n; c0 += 32) {
         const int col0 = n_blk * p.block_n + c0;
         if (col0 >= p.N) break;  // uniform across the warp
         uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * p.block_n + c0), r);
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * acc_cols +
+                      (uint32_t)(sub * p.block_n + c0), r);
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
@@ -381,11 +434,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           }
         }
       }
+      }  // sub-block
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
-      acc ^= 1;
-      if (acc == 0) acc_phase ^= 1;
+      if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
     }
   }
 
@@ -471,20 +524,34 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
   p.block_k = SLAB_BYTES / eb;
   // Tile width: the widest of 256/128/64 that still gives every SM a tile.
   int bn = 256;
-  auto tiles = [&](int n) { return (long long)((g.M + BLOCK_M - 1) / BLOCK_M) * ((g.N + n - 1) / n); };
-  while (bn > 64 && (tiles(bn) < sm_count || bn / 2 >= g.N)) bn /= 2;
+  auto tiles = [&](int rows, int n) { return (long long)((g.M + rows - 1) / rows) * ((g.N + n - 1) / n); };
+  while (bn > 64 && (tiles(BLOCK_M, bn) < sm_count || bn / 2 >= g.N)) bn /= 2;
   p.block_n = bn;
-  p.num_m_blocks = (g.M + BLOCK_M - 1) / BLOCK_M;
+  // 256-row tiles (two accumulators sharing each B slab: a third less shared-memory
+  // fill traffic per flop, at the price of a single TMEM stage) once they still give
+  // every SM work; 128-row tiles with two TMEM stages otherwise.
+  const char* force = getenv("B2_TC_SUB_M");
+  p.sub_m = (bn == 256 && tiles(2 * BLOCK_M, bn) >= sm_count) ? 2 : 1;
+  if (force && (force[0] == '1' || (force[0] == '2' && bn == 256))) p.sub_m = force[0] - '0';
+  p.acc_stages = p.sub_m == 2 ? 1 : 2;
+  p.num_m_blocks = (g.M + p.sub_m * BLOCK_M - 1) / (p.sub_m * BLOCK_M);
   p.num_n_blocks = (g.N + bn - 1) / bn;
   p.num_k_blocks = (g.K + p.block_k - 1) / p.block_k;
   p.tmem_cols = 2 * bn < 32 ? 32 : 2 * bn;  // 128, 256 or 512: powers of two
+  {
+    const long long T = (long long)p.num_m_blocks * p.num_n_blocks;
+    const long long rem = T % sm_count;
+    p.split_from = (int)T;
+    if (p.sub_m == 2 && T > sm_count && rem > 0 && rem * 2 <= sm_count) p.split_from = (int)(T - rem);
+    p.num_items = (int)(p.split_from + 2 * (T - p.split_from));
+  }
   p.kind_tf32 = (eb == 4);
   p.a_mn = a_mn; p.b_mn = b_mn;
   const uint32_t fmt = (eb == 4) ? 2u : 1u;  // tf32 : bf16
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) |
             ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BLOCK_M >> 4) << 24);
   const int slab_elems = SLAB_BYTES / eb;
-  p.a_stage_bytes = BLOCK_M * SLAB_BYTES;
+  p.a_stage_bytes = p.sub_m * BLOCK_M * SLAB_BYTES;
   p.b_stage_bytes = bn * SLAB_BYTES;
   bool ok = true;
   // M/N-contiguous operands: 16-bit elements use the plain 128-byte swizzle (8 k-rows of
@@ -505,7 +572,7 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
     ok = ok && make_map(&plan->map_a, g.A, eb, g.M, g.K, lda, slab_elems, p.block_k, mn_atom32);
   } else {
     p.a_boxes = 1;
-    p.a_box_bytes = p.a_stage_bytes;
+    p.a_box_bytes = BLOCK_M * SLAB_BYTES;
     p.a_lbo = 16;
     p.a_sbo = 1024;
     p.a_kstep = KSTEP_BYTES;
@@ -547,8 +614,7 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
   p.aux_bf16 = g.in_type == T_BF16;
   p.epilogue = g.epilogue;
   p.alpha = g.alpha;
-  const long long nt = (long long)p.num_m_blocks * p.num_n_blocks;
-  plan->grid = (int)(nt < sm_count ? nt : sm_count);
+  plan->grid = p.num_items < sm_count ? p.num_items : sm_count;
   return plan;
 }
 
@@ -559,13 +625,18 @@ cudaError_t gemm_tc_launch(const TcPlan* plan, cudaStream_t stream, unsigned int
   int dev = 0;
   cudaGetDevice(&dev);
   if (!(attr_set >> (dev & 63) & 1ull)) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(gemm_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
     if (e != cudaSuccess) return e;
     attr_set |= 1ull << (dev & 63);
   }
   TcParams p = plan->p;
   p.status = status;
-  gemm_tc_kernel<<<plan->grid, NUM_THREADS, plan->smem, stream>>>(plan->map_a, plan->map_b, p);
+  if (p.sub_m == 2)
+    gemm_tc_kernel<2><<<plan->grid, NUM_THREADS, plan->smem, stream>>>(plan->map_a, plan->map_b, p);
+  else
+    gemm_tc_kernel<1><<<plan->grid, NUM_THREADS, plan->smem, stream>>>(plan->map_a, plan->map_b, p);
   return cudaGetLastError();
 }
 

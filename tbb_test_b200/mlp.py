@@ -150,6 +150,15 @@ class MLP:
         self._ck(self.lib.b2_train_step_host(self._h, x_ptr, ldx, t_ptr, ldt, C.byref(v)))
         return v.value
 
+    def train_step_host_async(self, x_ptr, ldx, t_ptr, ldt):
+        """Enqueue copy + step without waiting (at most two in flight)."""
+        self._ck(self.lib.b2_train_step_host_async(self._h, x_ptr, ldx, t_ptr, ldt))
+
+    def wait_loss(self):
+        v = C.c_double()
+        self._ck(self.lib.b2_wait_loss(self._h, C.byref(v)))
+        return v.value
+
     def update_weight(self, l):
         """allreduce + SGD of layer l (the reference's update_weight)."""
         self._ck(self.lib.b2_allreduce_sgd(self._h, l))

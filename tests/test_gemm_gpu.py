@@ -68,6 +68,36 @@ def test_bf16_tensor_core(dev, oracle, form, shape):
     assert rel_fro(c, ref) <= TOL["bf16_f32out"]
 
 
+# Shapes wide enough for the 256-row tile mode (two accumulators per CTA sharing each
+# B slab): an exact multiple of the tile grid, and a ragged one whose tile count leaves
+# a partial last wave that is handed out as 128-row halves.
+BIG_SHAPES = [(4096, 4096, 192), (7944, 4096, 136)]
+
+
+@pytest.mark.parametrize("prec", ["bf16", "tf32"])
+@pytest.mark.parametrize("shape", BIG_SHAPES, ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("form", list(FORMS))
+def test_large_tile_mode(dev, oracle, form, shape, prec):
+    from tbb_test_b200 import _capi as K
+    m, n, k = shape
+    ta, tb, a, b = operands(oracle, form, m, n, k, 81)
+    before = dev.launch_counts()[1]
+    c = dev.sgemm_host(K.PREC_BF16 if prec == "bf16" else K.PREC_TF32, ta, tb, a, b)
+    assert dev.launch_counts()[1] == before + 1, "tensor-core kernel was not used"
+    oracle.use_openblas()
+    try:
+        if prec == "bf16":
+            ref = oracle.sgemm(ta, tb, oracle.round_bf16(a), oracle.round_bf16(b))
+        else:
+            ref = oracle.sgemm(ta, tb, a, b)
+    finally:
+        oracle.use_builtin_gemm()
+    # per-row check as well, so that a wrong or missing 128-row block cannot hide in the norm
+    assert rel_fro(c, ref) <= (TOL["bf16_f32out"] if prec == "bf16" else TOL["tf32"])
+    row_err = np.linalg.norm(c - ref, axis=1) / np.maximum(np.linalg.norm(ref, axis=1), 1e-30)
+    assert row_err.max() <= (1e-4 if prec == "bf16" else 4e-3)
+
+
 @pytest.mark.parametrize("prec", ["fp32", "tf32", "bf16"])
 @pytest.mark.parametrize("shape", [(256, 512, 256), (104, 72, 136)], ids=lambda s: "x".join(map(str, s)))
 def test_relu_and_mask_epilogues(dev, oracle, prec, shape):

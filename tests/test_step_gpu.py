@@ -1,13 +1,29 @@
 """GPU parity of the whole training step against the CPU oracle, through the C ABI.
 
-Tolerances (relative Frobenius error per tensor, after 10 SGD steps with lr 0.01
-on seeded inputs, compared on activations, propagated gradients, weight gradients
-of the last step and the weight change W10 - W0):
-  fp32  2e-5  against the fp32 oracle (only the order of fp32 additions differs)
-  tf32  4e-3  against the fp32 oracle (10-bit operand mantissas)
-  bf16  3e-2  against the fp32 oracle and against the oracle that rounds operands
-              to bf16 at the same points (8-bit operand mantissas; reduction order
-              and single-ulp rounding flips compound over the steps)
+Tolerances are relative Frobenius errors per tensor and are stated per precision
+and per kind of tensor, because two different mechanisms are at work:
+
+  state      activations, network output, loss, weights, and the weight change
+             W_k - W_0: errors are those of the operand precision (fp32 add order,
+             10-bit tf32 or 8-bit bf16 mantissas) and stay small.
+  gradients  dZ, dW of the last step, input gradient: in BASELINE mode they pass
+             through ReLU masks. An activation that is slightly positive in one
+             arithmetic and slightly negative in the other flips its mask, which
+             changes that gradient element by 100 %; with a fraction p of flipped
+             masks per layer the error is about sqrt(p * layers) - several percent
+             for bf16/tf32 against fp32 even after ONE step, although every single
+             GEMM agrees to 1e-7. They are therefore checked tightly where no flips
+             can occur (one step against the oracle that rounds operands at the same
+             points; REF mode, which has no ReLU) and loosely elsewhere.
+
+                        state     W_k - W_0   gradients
+  fp32  vs fp32 oracle  2e-5      2e-5        2e-5
+  tf32  vs fp32 oracle  1e-2      5e-2        1.5e-1   (REF mode, no masks: 1e-2)
+                        (the tensor core truncates fp32 operands to tf32, which shrinks
+                        every product by about 1e-3 on average: a bias that adds up
+                        layer by layer instead of averaging out)
+  bf16  vs fp32 oracle  2e-2      1e-1        2.5e-1
+  bf16 / tf32, one step, vs the oracle rounding operands identically: 2e-3 everywhere
 """
 import numpy as np
 import pytest
@@ -16,7 +32,26 @@ from helpers import make_problem, rel_fro
 
 pytestmark = pytest.mark.gpu
 
-TOL = {"fp32": 2e-5, "tf32": 4e-3, "bf16": 3e-2}
+TOL = {"fp32": dict(state=2e-5, total=2e-5, grad=2e-5),
+       "tf32": dict(state=1e-2, total=5e-2, grad=1.5e-1),
+       "bf16": dict(state=2e-2, total=1e-1, grad=2.5e-1)}
+SAME_ROUNDING_TOL = 2e-3
+
+
+def kind(name):
+    if name.startswith(("dz", "dw", "dinput")):
+        return "grad"
+    if name.startswith("dW_total"):
+        return "total"
+    return "state"
+
+
+def check(out, tol, skip=()):
+    for name, (a, b) in out.items():
+        if name in skip:
+            continue
+        t = tol if isinstance(tol, float) else tol[kind(name)]
+        assert rel_fro(a, b) <= t, f"{name}: {rel_fro(a, b):.3e} > {t}"
 
 
 def _prec(name):
@@ -63,18 +98,28 @@ def test_baseline_mode_10_steps(native, oracle, prec):
     from tbb_test_b200 import _capi as K
     nf = [256] * 6
     out, (total, tc) = run_pair(oracle, nf, 256, prec, K.MODE_BASELINE, 10, 0.01)
-    for name, (a, b) in out.items():
-        assert rel_fro(a, b) <= TOL[prec], f"{name}: {rel_fro(a, b):.3e}"
+    check(out, TOL[prec])
     if prec != "fp32":
         assert tc >= 10 * 15, "the step did not run on the tensor-core kernels"
 
 
-def test_bf16_against_rounding_oracle(native, oracle):
+@pytest.mark.parametrize("prec", ["bf16", "tf32"])
+def test_one_step_against_same_rounding_oracle(native, oracle, prec):
+    """One step from identical state against the oracle that rounds GEMM operands at the
+    same points (bf16: round-to-nearest-even at every store; tf32: the tensor core drops
+    the 13 low mantissa bits of fp32 operands): every tensor, gradients included."""
+    from tbb_test_b200 import _capi as K
+    nf = [256, 512, 256, 128]
+    rounding = oracle.ROUND_BF16 if prec == "bf16" else oracle.ROUND_TF32
+    out, _ = run_pair(oracle, nf, 384, prec, K.MODE_BASELINE, 1, 0.01, rounding=rounding)
+    check(out, SAME_ROUNDING_TOL)
+
+
+def test_bf16_three_steps_against_rounding_oracle(native, oracle):
     from tbb_test_b200 import _capi as K
     nf = [256, 512, 256, 128]
     out, _ = run_pair(oracle, nf, 384, "bf16", K.MODE_BASELINE, 3, 0.01, rounding=oracle.ROUND_BF16)
-    for name, (a, b) in out.items():
-        assert rel_fro(a, b) <= TOL["bf16"], f"{name}: {rel_fro(a, b):.3e}"
+    check(out, dict(state=5e-3, total=3e-2, grad=1e-1))
 
 
 @pytest.mark.parametrize("prec", ["fp32", "tf32"])
@@ -84,8 +129,7 @@ def test_ref_mode_matches_reference_semantics(native, oracle, prec):
     from tbb_test_b200 import _capi as K
     nf = [128, 256, 128, 64]
     out, _ = run_pair(oracle, nf, 200, prec, K.MODE_REF, 4, 1e-6)
-    for name, (a, b) in out.items():
-        assert rel_fro(a, b) <= TOL[prec], f"{name}: {rel_fro(a, b):.3e}"
+    check(out, TOL["fp32"] if prec == "fp32" else dict(state=1e-2, total=1e-2, grad=1e-2))
 
 
 def test_reference_topology_with_unit_tail(native, oracle):
@@ -95,8 +139,7 @@ def test_reference_topology_with_unit_tail(native, oracle):
     for prec in ("fp32", "bf16"):
         out, _ = run_pair(oracle, nf, 96, prec, K.MODE_REF, 2, 1e-8,
                           rounding=oracle.ROUND_BF16 if prec == "bf16" else None)
-        for name, (a, b) in out.items():
-            assert rel_fro(a, b) <= TOL[prec], f"{prec} {name}: {rel_fro(a, b):.3e}"
+        check(out, TOL["fp32"] if prec == "fp32" else SAME_ROUNDING_TOL)
 
 
 @pytest.mark.parametrize("kw", [dict(overlap=False), dict(use_graph=True), dict(collect_timing=True),
@@ -107,10 +150,7 @@ def test_schedule_variants_agree(native, oracle, kw):
     from tbb_test_b200 import _capi as K
     nf = [128, 256, 128]
     out, _ = run_pair(oracle, nf, 128, "fp32", K.MODE_BASELINE, 5, 0.01, **kw)
-    for name, (a, b) in out.items():
-        if name == "dinput" and kw.get("input_grad") is False:
-            continue
-        assert rel_fro(a, b) <= TOL["fp32"], f"{name}: {rel_fro(a, b):.3e}"
+    check(out, TOL["fp32"], skip=("dinput",) if kw.get("input_grad") is False else ())
 
 
 def test_allreduce_sgd_known_answer(native, oracle):
@@ -204,3 +244,58 @@ def test_bad_arguments_are_reported_not_fatal(native):
     assert m.lib.b2_download_weights(m._h, 0, None, 16) == K.ERR_INVALID
     assert m.lib.b2_step(m._h, -1) == K.ERR_INVALID
     m.close()
+
+
+@pytest.mark.parametrize("prec", ["fp32", "bf16"])
+def test_pipelined_host_fed_steps_equal_the_blocking_call(native, oracle, prec):
+    """b2_train_step_host_async/b2_wait_loss (copy of step i+1 overlapped with step i, two
+    input slots) computes exactly what a sequence of blocking b2_train_step_host calls
+    computes, on a stream of different batches."""
+    import ctypes as C
+    from tbb_test_b200 import _capi as K
+    from tbb_test_b200.mlp import MLP
+    nf, batch, steps = [128, 256, 64], 96, 5
+    ws, _, _ = make_problem(oracle, nf, batch)
+    xs = [oracle.fill_normal(batch, nf[0], 100 + i) for i in range(steps)]
+    ts = [oracle.fill_sign(batch, nf[-1], 200 + i) for i in range(steps)]
+    fp = C.POINTER(C.c_float)
+
+    def fresh():
+        m = MLP(nf, batch, precision=_prec(prec), lr=0.02)
+        for l in range(2):
+            m.upload_weights(l, ws[l])
+        return m
+
+    a, b = fresh(), fresh()
+    loss_a = [a.train_step_host(xs[i].ctypes.data_as(fp), nf[0], ts[i].ctypes.data_as(fp), nf[-1])
+              for i in range(steps)]
+    loss_b = []
+    for i in range(steps):
+        b.train_step_host_async(xs[i].ctypes.data_as(fp), nf[0], ts[i].ctypes.data_as(fp), nf[-1])
+        if i >= 1:
+            loss_b.append(b.wait_loss())
+    loss_b.append(b.wait_loss())
+    # the loss is summed with floating-point atomics: equal up to the order of additions
+    assert np.allclose(loss_a, loss_b, rtol=1e-12, atol=0)
+    for l in range(2):
+        assert np.array_equal(a.weights(l), b.weights(l))
+    # a third step in flight is refused, and so is b2_step while steps are pending
+    b.train_step_host_async(xs[0].ctypes.data_as(fp), nf[0], ts[0].ctypes.data_as(fp), nf[-1])
+    b.train_step_host_async(xs[1].ctypes.data_as(fp), nf[0], ts[1].ctypes.data_as(fp), nf[-1])
+    assert b.lib.b2_train_step_host_async(b._h, xs[2].ctypes.data_as(fp), nf[0], None, 0) == K.ERR_STATE
+    assert b.lib.b2_step(b._h, 1) == K.ERR_STATE
+    b.wait_loss()
+    b.wait_loss()
+    assert b.lib.b2_wait_loss(b._h, None) == K.ERR_STATE
+    # the loss decreases over a few steps of the same batch through the oracle's eyes
+    orc = oracle.Oracle(nf, batch, mode=oracle.MODE_BASELINE, lr=0.02,
+                        rounding=oracle.ROUND_BF16 if prec == "bf16" else oracle.ROUND_NONE)
+    for l in range(2):
+        orc.set_weights(l, ws[l])
+    orc.set_input(xs[0])
+    orc.set_target(ts[0])
+    orc.step(1)
+    assert abs(loss_a[0] - orc.loss()) <= 1e-3 * abs(orc.loss())
+    a.close()
+    b.close()
+    orc.close()
