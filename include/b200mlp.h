@@ -176,6 +176,25 @@ int b2_sgemm(b2_handle* h, int precision, int transa, int transb, int m, int n, 
              size_t ldc);
 int b2_sync(b2_handle* h);
 
+/* No counterpart in the reference. The bf16 tensor-core GEMM (same call meaning as
+ * b2_sgemm, alpha = 1, beta = 0) on fp32 DEVICE operands, for callers that must not
+ * allocate device memory: programs that gave all of it to their own pool, where a
+ * library's cudaMalloc can fail or stall, and latency-critical paths that cannot take
+ * the device-wide synchronisation cudaMalloc/cudaFree imply. It needs no handle and
+ * calls no cudaMalloc/cudaFree: the bf16 operand copies and the kernel's status word
+ * live in a fixed __device__ array of 16 MiB + 256 bytes that every GPU loading the
+ * library holds until the process exits. Limits: op(A) and op(B) may each hold at most
+ * B2_NOALLOC_MAX_OPERAND_ELEMS elements (larger ones return B2_ERR_UNSUPPORTED), and
+ * pointers / leading dimensions must be 16-byte aligned. The array is shared by all
+ * calls and keeps the previous call's contents: calls whose GPU work overlaps race.
+ * The first call on a device looks up the array's address and should be made outside
+ * stream capture. `stream` is a cudaStream_t (NULL = default stream); the call returns
+ * after the result is in `c`. b2_noalloc_last_error() has the text of a failure. */
+#define B2_NOALLOC_MAX_OPERAND_ELEMS (4u * 1024u * 1024u)
+int b2_gemm_bf16_noalloc(int transa, int transb, int m, int n, int k, const float* a, size_t lda,
+                         const float* b, size_t ldb, float* c, size_t ldc, void* stream);
+const char* b2_noalloc_last_error(void);
+
 /* update_weight (mlp_omp.cc:297-323) on layer `l`: sum weight_grads[l] over all
  * ranks, then w = fma(-lr, sum, w). The reference's known-answer test
  * (mlp_omp.cc:325-373) runs through this call. */

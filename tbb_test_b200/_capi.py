@@ -17,6 +17,7 @@ DTYPE_F32, DTYPE_BF16 = 0, 1
 EPI_NONE, EPI_RELU, EPI_MASK = 0, 1, 2
 T_FWD, T_WGT_GRAD, T_BWD, T_WGT_UPDATE, T_ALLREDUCE, T_NUM = 0, 1, 2, 3, 4, 5
 NCCL_ID_BYTES = 128
+NOALLOC_MAX_OPERAND_ELEMS = 4 * 1024 * 1024
 
 _fp = C.POINTER(C.c_float)
 _dp = C.POINTER(C.c_double)
@@ -64,6 +65,9 @@ SYMBOLS = {
     "b2_sgemm": (C.c_int, [_H, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_void_p,
                            C.c_size_t, C.c_void_p, C.c_size_t, C.c_float, C.c_void_p, C.c_size_t]),
     "b2_sync": (C.c_int, [_H]),
+    "b2_gemm_bf16_noalloc": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_size_t,
+                                       C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "b2_noalloc_last_error": (C.c_char_p, []),
     "b2_allreduce_sgd": (C.c_int, [_H, C.c_int]),
     "b2_allreduce_bench": (C.c_int, [_H, C.c_size_t, C.c_int, C.c_int, C.c_int, _dp, _dp]),
     "b2_get_timing": (C.c_int, [_H, _dp, _dp, C.POINTER(C.c_longlong)]),
