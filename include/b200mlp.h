@@ -95,7 +95,8 @@ int b2_config_default(b2_config* cfg);
 /* Library version string and the CUDA architecture it was built for. */
 const char* b2_version(void);
 
-/* Root rank: create the id every rank passes in b2_config.nccl_unique_id. */
+/* Root rank: create the id every rank passes in b2_config.nccl_unique_id. One id
+ * founds one communicator: every set of handles created together needs a fresh id. */
 int b2_nccl_unique_id(void* out_bytes);
 
 /* Allocation phase of main (mlp_omp.cc:390-409): device buffers for weights,

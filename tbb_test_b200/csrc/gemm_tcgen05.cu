@@ -29,6 +29,7 @@
 // releases its TMEM and returns.
 #include <cuda.h>
 
+#include <cmath>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -54,6 +55,8 @@ struct TcParams {
   int acc_stages;
   int num_items;         // work items: whole tiles, then the last partial wave cut in 128-row halves
   int split_from;        // first tile that is cut in halves
+  int raster_m;          // row blocks per band of the tile order (L2 reuse, see decode_item)
+  int pair;              // 1: CTA-pair kernel (cta_group::2), 256 x 256 tile per pair
   int stages;
   int tmem_cols;
   uint32_t idesc;
@@ -166,6 +169,59 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// ---- CTA-pair (cta_group::2) forms
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of `local_addr` (a shared::cta address) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// TMA load whose completion bytes are credited to an mbarrier that may live in the peer
+// CTA of the pair (`mbar_cluster_addr` is a shared::cluster address). No multicast: the
+// data lands in the issuing CTA's own shared memory only.
+__device__ __forceinline__ void tma_load_2d_pair(const CUtensorMap* map, uint32_t mbar_cluster_addr, void* dst,
+                                                 int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(mbar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+// commit of a pair's MMAs: arrives on the barrier at the same offset in both CTAs
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(smem_u32(bar)), "h"((uint16_t)3)
+      : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate, int tf32) {
+  if (tf32) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+
 // 64-bit shared-memory matrix descriptor (version 1) for a 128-byte-swizzled slab.
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo, uint32_t layout) {
   uint64_t d = 0;
@@ -183,22 +239,31 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 }
 
 // Work item -> (first row, number of 128-row sub-blocks, column block). Tiles are
-// numbered with the row block fastest; tiles from p.split_from on are handed out as
-// two 128-row halves so that the last, partial wave of a persistent grid costs half
-// a tile time instead of a whole one.
+// numbered band by band: a band is `raster_m` row blocks tall and spans all column
+// blocks, row block fastest inside it, so that the ~148 tiles in flight at any time
+// cover a roughly square patch of C and share their A and B slabs in L2 (a wave that
+// is one row-block column tall re-fetches A from DRAM for every column block).
+// Tiles from split_from on are handed out as two 128-row halves so that the last,
+// partial wave of a persistent grid costs half a tile time instead of a whole one.
 struct Item {
   int m0, sub, n_blk;
 };
 template <int SUB_M>
-__device__ __forceinline__ Item decode_item(int w, int split_from, int num_m_blocks, int M) {
+__device__ __forceinline__ Item decode_item(int w, int split_from, int num_m_blocks, int num_n_blocks, int raster_m,
+                                            int M) {
   int tile = w, half = -1;
   if (SUB_M == 2 && w >= split_from) {
     tile = split_from + ((w - split_from) >> 1);
     half = (w - split_from) & 1;
   }
   Item it;
-  it.n_blk = tile / num_m_blocks;
-  it.m0 = (tile % num_m_blocks) * (SUB_M * BLOCK_M);
+  const int band_tiles = raster_m * num_n_blocks;
+  const int band = tile / band_tiles;
+  const int in_band = tile - band * band_tiles;
+  const int m_base = band * raster_m;
+  const int band_rows = min(raster_m, num_m_blocks - m_base);
+  it.n_blk = in_band / band_rows;
+  it.m0 = (m_base + in_band % band_rows) * (SUB_M * BLOCK_M);
   it.sub = SUB_M;
   if (SUB_M == 2) {
     if (half >= 0) {
@@ -209,6 +274,85 @@ __device__ __forceinline__ Item decode_item(int w, int split_from, int num_m_blo
     }
   }
   return it;
+}
+
+// Epilogue of one 32-column chunk of one accumulator row: scale, ReLU or ReLU-mask,
+// convert, store (16-byte vectors when the chunk lies fully inside the matrix).
+__device__ __forceinline__ void epilogue_chunk(const TcParams& p, int row, bool row_ok, int col0,
+                                               const uint32_t (&r)[32]) {
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+  const bool full = (col0 + 32 <= p.N);
+  if (p.epilogue == EPI_RELU) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
+  } else if (p.epilogue == EPI_MASK && row_ok) {
+    if (p.aux_bf16) {
+      const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(p.aux) + (long long)row * p.ldaux + col0;
+      if (full) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 u = __ldg(reinterpret_cast<const uint4*>(x) + j);
+          const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            // a bf16 is positive iff it is non-zero with the sign bit clear
+            uint32_t lo = w[t] & 0xFFFFu, hi = w[t] >> 16;
+            if (!(lo != 0 && lo < 0x8000u)) v[j * 8 + t * 2] = 0.f;
+            if (!(hi != 0 && hi < 0x8000u)) v[j * 8 + t * 2 + 1] = 0.f;
+          }
+        }
+      } else {
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < p.N && !(__bfloat162float(x[j]) > 0.f)) v[j] = 0.f;
+      }
+    } else {
+      const float* x = static_cast<const float*>(p.aux) + (long long)row * p.ldaux + col0;
+      if (full) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float4 u = __ldg(reinterpret_cast<const float4*>(x) + j);
+          if (!(u.x > 0.f)) v[j * 4 + 0] = 0.f;
+          if (!(u.y > 0.f)) v[j * 4 + 1] = 0.f;
+          if (!(u.z > 0.f)) v[j * 4 + 2] = 0.f;
+          if (!(u.w > 0.f)) v[j * 4 + 3] = 0.f;
+        }
+      } else {
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < p.N && !(x[j] > 0.f)) v[j] = 0.f;
+      }
+    }
+  }
+  if (row_ok) {
+    if (p.out_bf16) {
+      __nv_bfloat16* c = static_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
+      if (full) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 o;
+          o.x = pack_bf16(v[j * 8 + 0], v[j * 8 + 1]);
+          o.y = pack_bf16(v[j * 8 + 2], v[j * 8 + 3]);
+          o.z = pack_bf16(v[j * 8 + 4], v[j * 8 + 5]);
+          o.w = pack_bf16(v[j * 8 + 6], v[j * 8 + 7]);
+          reinterpret_cast<uint4*>(c)[j] = o;
+        }
+      } else {
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < p.N) c[j] = __float2bfloat16_rn(v[j]);
+      }
+    } else {
+      float* c = static_cast<float*>(p.C) + (long long)row * p.ldc + col0;
+      if (full) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          reinterpret_cast<float4*>(c)[j] = make_float4(v[j * 4], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
+      } else {
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < p.N) c[j] = v[j];
+      }
+    }
+  }
 }
 
 // ------------------------------------------------------------------------ kernel
@@ -266,7 +410,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       uint32_t phase = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < num_items && ok; w += gridDim.x) {
-        const Item it = decode_item<SUB_M>(w, p.split_from, p.num_m_blocks, p.M);
+        const Item it = decode_item<SUB_M>(w, p.split_from, p.num_m_blocks, p.num_n_blocks, p.raster_m, p.M);
         const uint32_t a_bytes = (uint32_t)it.sub * (BLOCK_M * SLAB_BYTES);
         for (int kb = 0; kb < p.num_k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, 1u)) { ok = false; break; }
@@ -310,7 +454,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < num_items && ok; w += gridDim.x) {
-        const Item it = decode_item<SUB_M>(w, p.split_from, p.num_m_blocks, p.M);
+        const Item it = decode_item<SUB_M>(w, p.split_from, p.num_m_blocks, p.num_n_blocks, p.raster_m, p.M);
         if (!mbar_wait(&acc_empty_bar[acc], acc_phase ^ 1, abort_flag, p.status, 2u)) { ok = false; break; }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + (uint32_t)acc * acc_cols;
@@ -346,7 +490,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int w = blockIdx.x; w < num_items; w += gridDim.x) {
-      const Item it = decode_item<SUB_M>(w, p.split_from, p.num_m_blocks, p.M);
+      const Item it = decode_item<SUB_M>(w, p.split_from, p.num_m_blocks, p.num_n_blocks, p.raster_m, p.M);
       const int n_blk = it.n_blk;
       if (!mbar_wait(&acc_full_bar[acc], acc_phase, abort_flag, p.status, 4u)) break;
       tc_fence_after();
@@ -360,79 +504,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         uint32_t r[32];
         tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * acc_cols +
                       (uint32_t)(sub * p.block_n + c0), r);
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
-        const bool full = (col0 + 32 <= p.N);
-        if (p.epilogue == EPI_RELU) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
-        } else if (p.epilogue == EPI_MASK && row_ok) {
-          if (p.aux_bf16) {
-            const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(p.aux) + (long long)row * p.ldaux + col0;
-            if (full) {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                uint4 u = __ldg(reinterpret_cast<const uint4*>(x) + j);
-                const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                  // a bf16 is positive iff it is non-zero with the sign bit clear
-                  uint32_t lo = w[t] & 0xFFFFu, hi = w[t] >> 16;
-                  if (!(lo != 0 && lo < 0x8000u)) v[j * 8 + t * 2] = 0.f;
-                  if (!(hi != 0 && hi < 0x8000u)) v[j * 8 + t * 2 + 1] = 0.f;
-                }
-              }
-            } else {
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N && !(__bfloat162float(x[j]) > 0.f)) v[j] = 0.f;
-            }
-          } else {
-            const float* x = static_cast<const float*>(p.aux) + (long long)row * p.ldaux + col0;
-            if (full) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                float4 u = __ldg(reinterpret_cast<const float4*>(x) + j);
-                if (!(u.x > 0.f)) v[j * 4 + 0] = 0.f;
-                if (!(u.y > 0.f)) v[j * 4 + 1] = 0.f;
-                if (!(u.z > 0.f)) v[j * 4 + 2] = 0.f;
-                if (!(u.w > 0.f)) v[j * 4 + 3] = 0.f;
-              }
-            } else {
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N && !(x[j] > 0.f)) v[j] = 0.f;
-            }
-          }
-        }
-        if (row_ok) {
-          if (p.out_bf16) {
-            __nv_bfloat16* c = static_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
-            if (full) {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                uint4 o;
-                o.x = pack_bf16(v[j * 8 + 0], v[j * 8 + 1]);
-                o.y = pack_bf16(v[j * 8 + 2], v[j * 8 + 3]);
-                o.z = pack_bf16(v[j * 8 + 4], v[j * 8 + 5]);
-                o.w = pack_bf16(v[j * 8 + 6], v[j * 8 + 7]);
-                reinterpret_cast<uint4*>(c)[j] = o;
-              }
-            } else {
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N) c[j] = __float2bfloat16_rn(v[j]);
-            }
-          } else {
-            float* c = static_cast<float*>(p.C) + (long long)row * p.ldc + col0;
-            if (full) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                reinterpret_cast<float4*>(c)[j] = make_float4(v[j * 4], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
-            } else {
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N) c[j] = v[j];
-            }
-          }
-        }
+        epilogue_chunk(p, row, row_ok, col0, r);
       }
       }  // sub-block
       tc_fence_before();
@@ -448,6 +520,173 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)p.tmem_cols)
+                 : "memory");
+  }
+}
+
+// ------------------------------------------------------ kernel, CTA-pair variant
+//
+// Two CTAs of a cluster (two neighbouring SMs) work on one 256 x 256 tile with
+// tcgen05.mma.cta_group::2: CTA r of the pair holds rows [r*128, r*128+128) of the A
+// slab and the r-th 128-column half of the B slab, the leader CTA (rank 0) issues
+// every MMA, and each CTA's TMEM receives its own 128 rows x 256 columns of the
+// accumulator. Each SM's shared memory then feeds 4 KB of A + 4 KB of B per MMA
+// instead of 4 KB + 8 KB, and is filled with 32 KB instead of 48 KB per k-block,
+// with two TMEM stages kept for epilogue overlap.
+//
+// Barriers: full[s] lives in the leader and collects the bytes of both CTAs' loads;
+// empty[s] and acc_full[a] exist in both CTAs and are signalled by one multicast
+// tcgen05.commit; acc_empty[a] lives in the leader and counts the epilogue warps of
+// both CTAs (the peer's arrive remotely). A cluster barrier after initialisation keeps
+// remote signals away from uninitialised barriers, one before exit keeps either CTA's
+// shared memory and TMEM alive while the other may still touch it.
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                    const __grid_constant__ TcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[MAX_STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[MAX_STAGES];
+  __shared__ __align__(8) uint64_t acc_full_bar[2];
+  __shared__ __align__(8) uint64_t acc_empty_bar[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_s;
+
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t stage_bytes = p.a_stage_bytes + p.b_stage_bytes;  // per CTA
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  volatile int* abort_flag = &abort_s;
+
+  if (threadIdx.x == 0) {
+    abort_s = 0;
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full_bar[a], 1);
+      mbar_init(&acc_empty_bar[a], 8);  // four epilogue warps in each CTA of the pair
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tma_a) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tma_b) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)),
+                 "r"((uint32_t)p.tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+  const int num_tiles = p.num_m_blocks * p.num_n_blocks;  // 256 x 256 tiles
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+        const Item it = decode_item<2>(t, num_tiles, p.num_m_blocks, p.num_n_blocks, p.raster_m, 1 << 30);
+        const int m0 = it.m0 + (int)rank * BLOCK_M;                   // this CTA's rows of A
+        const int n0 = it.n_blk * p.block_n + (int)rank * (p.block_n / 2);  // this CTA's half of B
+        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, 1u)) { ok = false; break; }
+          uint8_t* sa = smem + (size_t)stage * stage_bytes;
+          uint8_t* sb = sa + p.a_stage_bytes;
+          if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * stage_bytes);  // both CTAs' bytes
+          const uint32_t full_addr = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          const int k0 = kb * p.block_k;
+          if (p.a_mn) {
+            for (int b = 0; b < p.a_boxes; ++b)
+              tma_load_2d_pair(&tma_a, full_addr, sa + (size_t)b * p.a_box_bytes, m0 + b * p.a_box_mn, k0);
+          } else {
+            tma_load_2d_pair(&tma_a, full_addr, sa, k0, m0);
+          }
+          if (p.b_mn) {
+            for (int b = 0; b < p.b_boxes; ++b)
+              tma_load_2d_pair(&tma_b, full_addr, sb + (size_t)b * p.b_box_bytes, n0 + b * p.b_box_mn, k0);
+          } else {
+            tma_load_2d_pair(&tma_b, full_addr, sb, k0, n0);
+          }
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        const unsigned long long t0 = globaltimer();
+        while (globaltimer() - t0 < 2000000ull) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ----------------------------------------------- MMA issuer (leader CTA only)
+    if (lane == 0 && rank == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+        if (!mbar_wait(&acc_empty_bar[acc], acc_phase ^ 1, abort_flag, p.status, 2u)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * p.block_n);
+        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 3u)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + (size_t)stage * stage_bytes);
+          const uint32_t sb = sa + p.a_stage_bytes;
+#pragma unroll
+          for (int ks = 0; ks < KSTEPS; ++ks) {
+            const uint64_t adesc = make_smem_desc(sa + ks * p.a_kstep, p.a_lbo, p.a_sbo, p.a_layout);
+            const uint64_t bdesc = make_smem_desc(sb + ks * p.b_kstep, p.b_lbo, p.b_sbo, p.b_layout);
+            tc_mma_pair(tmem_d, adesc, bdesc, p.idesc, (uint32_t)((kb | ks) != 0), p.kind_tf32);
+          }
+          tc_commit_pair(&empty_bar[stage]);
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        tc_commit_pair(&acc_full_bar[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int q = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = pair; t < num_tiles; t += num_pairs) {
+      const Item it = decode_item<2>(t, num_tiles, p.num_m_blocks, p.num_n_blocks, p.raster_m, 1 << 30);
+      if (!mbar_wait(&acc_full_bar[acc], acc_phase, abort_flag, p.status, 4u)) break;
+      tc_fence_after();
+      const int row = it.m0 + (int)rank * BLOCK_M + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      for (int c0 = 0; c0 < p.block_n; c0 += 32) {
+        const int col0 = it.n_blk * p.block_n + c0;
+        if (col0 >= p.N) break;
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * p.block_n + c0), r);
+        epilogue_chunk(p, row, row_ok, col0, r);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty_bar[acc]), 0));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)p.tmem_cols)
                  : "memory");
   }
 }
@@ -533,26 +772,43 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
   const char* force = getenv("B2_TC_SUB_M");
   p.sub_m = (bn == 256 && tiles(2 * BLOCK_M, bn) >= sm_count) ? 2 : 1;
   if (force && (force[0] == '1' || (force[0] == '2' && bn == 256))) p.sub_m = force[0] - '0';
-  p.acc_stages = p.sub_m == 2 ? 1 : 2;
+  // CTA pairs: a 256 x 256 tile per pair of SMs once there is a tile for every pair
+  {
+    const char* pe = getenv("B2_TC_PAIR");
+    const bool want = pe ? (pe[0] == '1') : false;
+    p.pair = (want && bn == 256 && tiles(2 * BLOCK_M, bn) >= sm_count / 2) ? 1 : 0;
+    if (p.pair) p.sub_m = 2;  // tile rows for the work decomposition: 128 per CTA of the pair
+  }
+  p.acc_stages = (p.sub_m == 2 && !p.pair) ? 1 : 2;
   p.num_m_blocks = (g.M + p.sub_m * BLOCK_M - 1) / (p.sub_m * BLOCK_M);
   p.num_n_blocks = (g.N + bn - 1) / bn;
   p.num_k_blocks = (g.K + p.block_k - 1) / p.block_k;
   p.tmem_cols = 2 * bn < 32 ? 32 : 2 * bn;  // 128, 256 or 512: powers of two
   {
+    // band height that makes a wave of sm_count tiles about square in elements of C
+    const double aspect = (double)bn / (p.sub_m * BLOCK_M);
+    int rm = (int)(sqrt((double)sm_count * aspect) + 0.5);
+    if (const char* r = getenv("B2_TC_RASTER")) rm = atoi(r);
+    if (rm < 1) rm = 1;
+    if (rm > p.num_m_blocks) rm = p.num_m_blocks;
+    p.raster_m = rm;
+  }
+  {
     const long long T = (long long)p.num_m_blocks * p.num_n_blocks;
     const long long rem = T % sm_count;
     p.split_from = (int)T;
-    if (p.sub_m == 2 && T > sm_count && rem > 0 && rem * 2 <= sm_count) p.split_from = (int)(T - rem);
+    if (p.sub_m == 2 && !p.pair && T > sm_count && rem > 0 && rem * 2 <= sm_count) p.split_from = (int)(T - rem);
     p.num_items = (int)(p.split_from + 2 * (T - p.split_from));
   }
   p.kind_tf32 = (eb == 4);
   p.a_mn = a_mn; p.b_mn = b_mn;
   const uint32_t fmt = (eb == 4) ? 2u : 1u;  // tf32 : bf16
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) |
-            ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BLOCK_M >> 4) << 24);
+            ((uint32_t)(bn >> 3) << 17) | ((uint32_t)((p.pair ? 2 * BLOCK_M : BLOCK_M) >> 4) << 24);
   const int slab_elems = SLAB_BYTES / eb;
-  p.a_stage_bytes = p.sub_m * BLOCK_M * SLAB_BYTES;
-  p.b_stage_bytes = bn * SLAB_BYTES;
+  const int cta_bn = p.pair ? bn / 2 : bn;  // B rows (columns of C) held by one CTA
+  p.a_stage_bytes = (p.pair ? 1 : p.sub_m) * BLOCK_M * SLAB_BYTES;
+  p.b_stage_bytes = cta_bn * SLAB_BYTES;
   bool ok = true;
   // M/N-contiguous operands: 16-bit elements use the plain 128-byte swizzle (8 k-rows of
   // 128 B per 1024-byte group); 32-bit elements are only accepted in the variant that
@@ -580,7 +836,7 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
     ok = ok && make_map(&plan->map_a, g.A, eb, g.K, g.M, lda, p.block_k, BLOCK_M, false);
   }
   if (b_mn) {
-    p.b_boxes = bn / slab_elems;
+    p.b_boxes = cta_bn / slab_elems;
     p.b_box_mn = slab_elems;
     p.b_box_bytes = p.block_k * SLAB_BYTES;
     p.b_lbo = p.b_box_bytes;
@@ -595,7 +851,7 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
     p.b_sbo = 1024;
     p.b_kstep = KSTEP_BYTES;
     p.b_layout = 2;
-    ok = ok && make_map(&plan->map_b, g.B, eb, g.K, g.N, ldb, p.block_k, bn, false);
+    ok = ok && make_map(&plan->map_b, g.B, eb, g.K, g.N, ldb, p.block_k, cta_bn, false);
   }
   if (!ok) {
     delete plan;
@@ -615,6 +871,11 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
   p.epilogue = g.epilogue;
   p.alpha = g.alpha;
   plan->grid = p.num_items < sm_count ? p.num_items : sm_count;
+  if (p.pair) {
+    const int pairs = sm_count / 2;
+    const int T = p.num_m_blocks * p.num_n_blocks;
+    plan->grid = 2 * (T < pairs ? T : pairs);
+  }
   return plan;
 }
 
@@ -633,6 +894,27 @@ cudaError_t gemm_tc_launch(const TcPlan* plan, cudaStream_t stream, unsigned int
   }
   TcParams p = plan->p;
   p.status = status;
+  if (p.pair) {
+    static unsigned long long pair_attr_set = 0;
+    if (!(pair_attr_set >> (dev & 63) & 1ull)) {
+      cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
+      if (e != cudaSuccess) return e;
+      pair_attr_set |= 1ull << (dev & 63);
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(plan->grid);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = plan->smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel, plan->map_a, plan->map_b, p);
+  }
   if (p.sub_m == 2)
     gemm_tc_kernel<2><<<plan->grid, NUM_THREADS, plan->smem, stream>>>(plan->map_a, plan->map_b, p);
   else

@@ -1,0 +1,84 @@
+"""Worker of tests/test_multigpu_gpu.py: one rank (one GPU) of a data-parallel job.
+
+Runs the reference's allreduce+SGD known-answer test across the ranks and a few
+training steps, and checks both against the CPU oracle configured with the same
+number of ranks. Exits non-zero on any mismatch."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+from helpers import make_problem, rel_fro  # noqa: E402
+from oracle import oracle as O  # noqa: E402
+from tbb_test_b200 import _capi as K  # noqa: E402
+from tbb_test_b200.mlp import MLP, nccl_unique_id  # noqa: E402
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dist.init_process_group("gloo")  # only carries the NCCL id and the verdicts
+
+    def fresh_id():
+        # an NCCL unique id founds exactly one communicator: every handle gets its own
+        box = [nccl_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        return box[0]
+
+
+    # 1. the reference's self-check (mlp_omp.cc:325-373) with one GPU per socket
+    nrows, ncols = 256, 512
+    w, g, e = O.kat(world, nrows, ncols)
+    dev = MLP([ncols, nrows], 8 * world, rank=rank, world_size=world, device=local, lr=1.0, nccl_id=fresh_id())
+    dev.upload_weights(0, w[rank])
+    dev.upload_weight_grad(0, g[rank])
+    dev.update_weight(0)
+    got = dev.weights(0)
+    assert np.array_equal(got, e), f"rank {rank}: allreduce+SGD known-answer test failed"
+    ms, checksum = dev.allreduce_bench(1 << 20, K.DTYPE_F32, 2, 5)
+    ref = sum(O.fill_uniform(1, 4096, r, -1.0, 1.0).astype(np.float64).sum() for r in range(world))
+    assert abs(checksum - ref) <= 1e-3, (checksum, ref)
+    dev.close()
+
+    # 2. training steps: every precision, ragged batch split, against the oracle with `world` ranks
+    nf, batch, steps = [256, 512, 256, 128], 200 + world, 3
+    ws, x, t = make_problem(O, nf, batch)
+    for prec, rounding, tol in ((K.PREC_FP32, O.ROUND_NONE, dict(state=2e-5, grad=2e-5)),
+                                (K.PREC_BF16, O.ROUND_BF16, dict(state=5e-3, grad=1e-1))):
+        for overlap in (True, False):
+            dev = MLP(nf, batch, rank=rank, world_size=world, device=local, precision=prec, lr=0.01,
+                      nccl_id=fresh_id(), overlap=overlap)
+            orc = O.Oracle(nf, batch, nranks=world, mode=O.MODE_BASELINE, rounding=rounding, lr=0.01)
+            for l in range(3):
+                dev.upload_weights(l, ws[l])
+                orc.set_weights(l, ws[l])
+            dev.upload_input(x)
+            dev.upload_target(t)
+            orc.set_input(x)
+            orc.set_target(t)
+            dev.step(steps)
+            orc.step(steps)
+            b0, b1 = dev.rows
+            assert (b0, b1) == O.batch_range(batch, world, rank)
+            assert rel_fro(dev.activation(3), orc.activation(3)[b0:b1]) <= tol["state"]
+            for l in range(3):
+                assert rel_fro(dev.weights(l) - ws[l], orc.weights(l) - ws[l]) <= max(tol["state"], 3e-2 if prec else 0), l
+                assert rel_fro(dev.weight_grad(l), orc.weight_grad(l)) <= tol["grad"], l  # summed over ranks
+            loss = torch.tensor([dev.loss()], dtype=torch.float64)
+            dist.all_reduce(loss)
+            assert abs(loss.item() - orc.loss()) <= 2e-3 * abs(orc.loss())
+            dev.close()
+            orc.close()
+    dist.barrier()
+    dist.destroy_process_group()
+    print(f"rank {rank}: ok")
+
+
+if __name__ == "__main__":
+    main()
