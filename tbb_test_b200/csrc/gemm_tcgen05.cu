@@ -139,22 +139,6 @@ __device__ __forceinline__ void tc_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
 }
-__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                       uint32_t accumulate, int tf32) {
-  if (tf32) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-  } else {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-  }
-}
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -205,20 +189,45 @@ __device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
       ::"r"(smem_u32(bar)), "h"((uint16_t)3)
       : "memory");
 }
-__device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                            uint32_t accumulate, int tf32) {
-  if (tf32) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-  } else {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
+// One k-block (KSTEPS MMAs per 128-row sub-block) issued from precomputed descriptor
+// templates. A single thread issues every MMA of the CTA, so the instruction count
+// between two MMAs is what bounds the tensor pipe's duty cycle: the constant descriptor
+// fields are assembled once per kernel, and per MMA only the 14-bit start-address field
+// (address >> 4) is added in.
+template <int SUB_M, bool TF32, bool PAIR>
+__device__ __forceinline__ void issue_kblock(uint32_t tmem_d, uint64_t a_tmpl, uint64_t b_tmpl, uint32_t sa16,
+                                             uint32_t sb16, uint32_t a_step16, uint32_t b_step16, uint32_t idesc,
+                                             uint32_t block_n, int sub, bool first_kblock) {
+#pragma unroll
+  for (int ks = 0; ks < KSTEPS; ++ks) {
+    const uint64_t bdesc = b_tmpl + (uint64_t)(sb16 + ks * b_step16);
+    const uint32_t accumulate = (ks == 0) ? (first_kblock ? 0u : 1u) : 1u;
+#pragma unroll
+    for (int i = 0; i < SUB_M; ++i) {  // the 128-row sub-blocks share the B slab
+      if (i < sub) {
+        const uint64_t adesc = a_tmpl + (uint64_t)(sa16 + i * ((BLOCK_M * SLAB_BYTES) >> 4) + ks * a_step16);
+        const uint32_t d = tmem_d + (uint32_t)i * block_n;
+        if (PAIR) {
+          if (TF32)
+            asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                         "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+                         ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+          else
+            asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                         "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                         ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+        } else {
+          if (TF32)
+            asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                         "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+                         ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+          else
+            asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                         ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+        }
+      }
+    }
   }
 }
 
@@ -453,6 +462,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
+      const uint64_t a_tmpl = make_smem_desc(0, p.a_lbo, p.a_sbo, p.a_layout);
+      const uint64_t b_tmpl = make_smem_desc(0, p.b_lbo, p.b_sbo, p.b_layout);
+      const uint32_t smem16 = smem_u32(smem) >> 4, stage16 = stage_bytes >> 4, a_stage16 = p.a_stage_bytes >> 4;
+      const uint32_t a_step16 = p.a_kstep >> 4, b_step16 = p.b_kstep >> 4, idesc = p.idesc;
+      const uint32_t block_n = (uint32_t)p.block_n;
+      const bool tf32 = p.kind_tf32 != 0;
       for (int w = blockIdx.x; w < num_items && ok; w += gridDim.x) {
         const Item it = decode_item<SUB_M>(w, p.split_from, p.num_m_blocks, p.num_n_blocks, p.raster_m, p.M);
         if (!mbar_wait(&acc_empty_bar[acc], acc_phase ^ 1, abort_flag, p.status, 2u)) { ok = false; break; }
@@ -461,21 +476,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         for (int kb = 0; kb < p.num_k_blocks; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 3u)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + (size_t)stage * stage_bytes);
-          const uint32_t sb = sa + p.a_stage_bytes;
-#pragma unroll
-          for (int ks = 0; ks < KSTEPS; ++ks) {
-            const uint64_t bdesc = make_smem_desc(sb + ks * p.b_kstep, p.b_lbo, p.b_sbo, p.b_layout);
-#pragma unroll
-            for (int i = 0; i < SUB_M; ++i) {  // the 128-row sub-blocks share the B slab
-              if (i < it.sub) {
-                const uint64_t adesc = make_smem_desc(sa + i * (BLOCK_M * SLAB_BYTES) + ks * p.a_kstep, p.a_lbo,
-                                                      p.a_sbo, p.a_layout);
-                tc_mma(tmem_d + (uint32_t)(i * p.block_n), adesc, bdesc, p.idesc, (uint32_t)((kb | ks) != 0),
-                       p.kind_tf32);
-              }
-            }
-          }
+          const uint32_t sa16 = smem16 + (uint32_t)stage * stage16;
+          if (tf32)
+            issue_kblock<SUB_M, true, false>(tmem_d, a_tmpl, b_tmpl, sa16, sa16 + a_stage16, a_step16, b_step16,
+                                             idesc, block_n, it.sub, kb == 0);
+          else
+            issue_kblock<SUB_M, false, false>(tmem_d, a_tmpl, b_tmpl, sa16, sa16 + a_stage16, a_step16, b_step16,
+                                              idesc, block_n, it.sub, kb == 0);
           tc_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
@@ -630,6 +637,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
+      const uint64_t a_tmpl = make_smem_desc(0, p.a_lbo, p.a_sbo, p.a_layout);
+      const uint64_t b_tmpl = make_smem_desc(0, p.b_lbo, p.b_sbo, p.b_layout);
+      const uint32_t smem16 = smem_u32(smem) >> 4, stage16 = stage_bytes >> 4, a_stage16 = p.a_stage_bytes >> 4;
+      const uint32_t a_step16 = p.a_kstep >> 4, b_step16 = p.b_kstep >> 4, idesc = p.idesc;
+      const bool tf32 = p.kind_tf32 != 0;
       for (int t = pair; t < num_tiles && ok; t += num_pairs) {
         if (!mbar_wait(&acc_empty_bar[acc], acc_phase ^ 1, abort_flag, p.status, 2u)) { ok = false; break; }
         tc_fence_after();
@@ -637,14 +649,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         for (int kb = 0; kb < p.num_k_blocks; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 3u)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + (size_t)stage * stage_bytes);
-          const uint32_t sb = sa + p.a_stage_bytes;
-#pragma unroll
-          for (int ks = 0; ks < KSTEPS; ++ks) {
-            const uint64_t adesc = make_smem_desc(sa + ks * p.a_kstep, p.a_lbo, p.a_sbo, p.a_layout);
-            const uint64_t bdesc = make_smem_desc(sb + ks * p.b_kstep, p.b_lbo, p.b_sbo, p.b_layout);
-            tc_mma_pair(tmem_d, adesc, bdesc, p.idesc, (uint32_t)((kb | ks) != 0), p.kind_tf32);
-          }
+          const uint32_t sa16 = smem16 + (uint32_t)stage * stage16;
+          if (tf32)
+            issue_kblock<1, true, true>(tmem_d, a_tmpl, b_tmpl, sa16, sa16 + a_stage16, a_step16, b_step16, idesc,
+                                        0u, 1, kb == 0);
+          else
+            issue_kblock<1, false, true>(tmem_d, a_tmpl, b_tmpl, sa16, sa16 + a_stage16, a_step16, b_step16, idesc,
+                                         0u, 1, kb == 0);
           tc_commit_pair(&empty_bar[stage]);
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
