@@ -182,13 +182,94 @@ def measured_peaks():
         return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
 
 
+def allreduce_sweep(args, rank, world, local_rank):
+    """Configuration 2: fp32 buffers of 4 KB .. 1 GB (powers of two), U(-1,1) from seed = rank,
+    summed over all GPUs with the library's gradient allreduce; bus bandwidth
+    bytes * 2(G-1)/G / t per size (the reference counts the same bytes per socket for its
+    reduce-scatter + allgather, mlp_omp.cc:163,288). The CPU side is the reference's own ring
+    (update_weight) on host threads acting as sockets, on a bounded set of sizes."""
+    sizes = [1 << p for p in range(12, 31)]
+    if args.impl == "reference" or world < 2:
+        if rank != 0:
+            return 0
+        from oracle import oracle as O
+        cores = host_cores()
+        socks = 8 if cores >= 8 else 2
+        table = []
+        try:
+            R = O.RefLib()
+            for nbytes in (1 << 12, 1 << 16, 1 << 20, 1 << 24, 1 << 26):
+                ncols = 1008  # ld = 1024 floats
+                nrows = max(1, nbytes // 4 // ncols)
+                iters = 20 if nbytes <= (1 << 20) else 3
+                t = R.time_update_weight(socks, 1, nrows, ncols, iters)
+                real = nrows * ncols * 4
+                table.append({"bytes": real, "ms": t * 1e3, "busbw_gbs": real * 2 * (socks - 1) / socks / t / 1e9})
+            kind = "reference"
+        except Exception as e:  # no prebuilt reference on this machine
+            table, kind = [{"error": str(e)}], "unavailable"
+        best = max((r.get("busbw_gbs", 0.0) for r in table), default=0.0)
+        cpu = {"value": best, "unit": "GB/s", "cores": socks, "kind": kind,
+               "sample": f"reference update_weight (ring reduce-scatter + SGD + allgather), {socks} sockets x 1 "
+                         "thread on the host cores, sizes 4 KB .. 64 MB", "table": table}
+        line = {"impl": "reference", "metric": "allreduce_busbw", "value": best, "unit": "GB/s", "n_gpus": 0,
+                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": None, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": "c2: gradient allreduce sweep, fp32"}, "cpu_baseline": cpu,
+                "e2e": {"value": best, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
+        if args.impl != "reference":
+            line.pop("impl")
+            line["note"] = "the sweep needs 2 or more GPUs; only the CPU side was run"
+        print(json.dumps(line))
+        return 0
+
+    import torch
+    import torch.distributed as dist
+    from tbb_test_b200 import _capi as K
+    from tbb_test_b200.mlp import MLP, nccl_unique_id
+    torch.cuda.set_device(local_rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    box = [nccl_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    dev = MLP([16, 16], 16 * world, rank=rank, world_size=world, device=local_rank, nccl_id=box[0])
+    table = []
+    for nbytes in sizes:
+        iters = max(5, min(args.steps, 200 if nbytes <= (1 << 22) else 20))
+        torch.cuda.synchronize()
+        dist.barrier()
+        ms, _ = dev.allreduce_bench(nbytes // 4, K.DTYPE_F32, max(args.warmup, 3), iters)
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        table.append({"bytes": nbytes, "ms": ms, "busbw_gbs": nbytes * 2 * (world - 1) / world / (ms / 1e3) / 1e9})
+    launches = dev.launch_counts()[0]
+    dev.close()
+    if rank == 0:
+        top = table[-1]
+        line = {"metric": "allreduce_busbw", "value": top["busbw_gbs"], "unit": "GB/s", "n_gpus": world,
+                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": top["ms"],
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+                "data": "synthetic", "config": {"workload": f"c2: gradient allreduce sweep, fp32, {world} GPUs, "
+                                                "value = bus bandwidth at 1 GiB", "table": table},
+                "roofline": {"bound": "nvlink", "achieved": top["busbw_gbs"], "peak": 770.0, "unit": "GB/s",
+                             "frac": top["busbw_gbs"] / 770.0, "traffic": None,
+                             "peak_source": "measured peer copy per direction on this pool (900 nominal)"},
+                "cpu_baseline": None, "e2e": None, "gpu_launches": launches * world}
+        print(json.dumps(line))
+    dist.barrier()
+    dist.destroy_process_group()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS) + ["c2"],
+                    help="c2 = the gradient-allreduce sweep alone (needs 2 or more GPUs)")
     ap.add_argument("--precision", default="bf16", choices=["bf16", "tf32", "fp32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -197,6 +278,8 @@ def main():
 
     rank, world = env_int("RANK", 0), env_int("WORLD_SIZE", 1)
     local_rank = env_int("LOCAL_RANK", 0)
+    if args.workload == "c2":
+        return allreduce_sweep(args, rank, world, local_rank)
     nf, batch, winit, desc = WORKLOADS[args.workload]
     warmup = max(args.warmup, 3)
     L = len(nf) - 1

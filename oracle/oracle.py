@@ -279,6 +279,8 @@ class RefLib:
         L.ref_get_weight_grad.argtypes = [C.c_int, C.c_int, _fp, C.c_size_t]
         L.ref_get_activation.argtypes = [C.c_int, _fp, C.c_size_t]
         L.ref_update_weight.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, _fp, _fp, C.c_double]
+        L.ref_time_update_weight.restype = C.c_double
+        L.ref_time_update_weight.argtypes = [C.c_int] * 5
         L.ref_get_partition.argtypes = [C.c_int] * 5 + [_ip]
         L.ref_intra_socket_2d.argtypes = [C.c_int, C.c_int, C.c_double, C.c_int, C.c_int, C.c_int, _ip]
         L.ref_2dpartition.argtypes = [C.c_int, C.c_int, C.c_int, C.c_double, C.c_int, C.c_int, C.c_int,
@@ -322,6 +324,10 @@ class RefLib:
         self.L.ref_update_weight(n, nthreads_per_socket, nrows, ncols, w.ctypes.data_as(_fp),
                                  g.ctypes.data_as(_fp), alpha)
         return w
+
+    def time_update_weight(self, nsock, nthr, nrows, ncols, iters):
+        """Seconds per call of the reference's allreduce + SGD on (nsock*nrows) x ncols buffers."""
+        return self.L.ref_time_update_weight(nsock, nthr, nrows, ncols, iters)
 
     def _ints(self, fn, n, *args):
         out = (C.c_int * n)()

@@ -100,6 +100,35 @@ void ref_update_weight(int nsock, int nthr, int nrows, int ncols, float* w, cons
     memcpy(w + (size_t)i * ncols, W.rawData(i, 0), sizeof(float) * ncols);
 }
 
+// Seconds per call of the reference's update_weight (ring reduce-scatter + SGD +
+// allgather, mlp_omp.cc:297-323) on (nsock*nrows) x ncols buffers that stay allocated
+// across `iters` timed calls after one warm-up call: the CPU side of the allreduce sweep.
+double ref_time_update_weight(int nsock, int nthr, int nrows, int ncols, int iters) {
+  nsockets = nsock;
+  nthreads_per_socket = nthr;
+  nthreads = nsock * nthr;
+  omp_set_num_threads(nthreads);
+  Matrix<float, PAD> W(nsock * nrows, ncols), G(nsock * nrows, ncols), P(nsock * nrows, ncols);
+  const size_t n = (size_t)(nsock * nrows + PAD) * (ncols + PAD);
+#pragma omp parallel for
+  for (size_t i = 0; i < n; ++i) {
+    W.rawData()[i] = 0.f;
+    G.rawData()[i] = 1e-3f;
+    P.rawData()[i] = 0.f;
+  }
+  double t0 = 0;
+  for (int it = -1; it < iters; ++it) {
+    if (it == 0) t0 = dsecnd();
+    for (int i = 0; i < nthreads * 16; ++i) done_flags[i] = 0;
+#pragma omp parallel
+    {
+      done_flag_phase = 0;
+      update_weight(&W, &G, &P, 1e-10, 0, false, get_num_threads_per_socket(), get_thread_num_in_socket());
+    }
+  }
+  return (dsecnd() - t0) / iters;
+}
+
 // Partition.cc:34-51
 void ref_get_partition(int nsock, int work, int socket_id, int nthr, int tid, int* out2) {
   nsockets = nsock;
