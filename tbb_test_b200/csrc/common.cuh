@@ -34,7 +34,13 @@ struct GemmDesc {
   int epilogue;
   int in_type;   // ElemType of A, B and aux
   int out_type;  // ElemType of C
+  // Optional stream-K workspace of the tensor-core kernel (null = whole tiles per CTA):
+  // TC_WS_SLOT_BYTES per SM and one zero-initialised flag word per SM. GEMMs that share a
+  // workspace must not overlap on the GPU.
+  float* ws;
+  unsigned int* ws_flags;
 };
+constexpr size_t TC_WS_SLOT_BYTES = 2 * 128 * 256 * sizeof(float);
 
 // CUDA-core GEMM for any shape, stride and alignment (fp32 accumulate).
 cudaError_t gemm_simt_launch(const GemmDesc& g, cudaStream_t stream);

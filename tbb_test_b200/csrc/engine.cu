@@ -57,6 +57,8 @@ struct b2_handle {
   size_t stage_elems = 0;
   double* loss_dev = nullptr;  // [2]: one accumulator per input slot
   unsigned int* status_dev = nullptr;
+  float* tc_ws = nullptr;           // stream-K workspace shared by this handle's GEMMs (they
+  unsigned int* tc_ws_flags = nullptr;  // all run on the main stream, one after the other)
   std::vector<cudaEvent_t> ev_wgrad, ev_dgrad, ev_upd;
   std::vector<char> upd_pending;
   cudaEvent_t ev_t0 = nullptr, ev_t1 = nullptr, ev_join = nullptr, ev_fork = nullptr;
@@ -123,6 +125,8 @@ void batch_range(int batch, int world, int rank, int* b, int* e) {
 }
 
 int make_site(b2_handle* h, Site& s, bool want_tc) {
+  s.d.ws = h->tc_ws;
+  s.d.ws_flags = h->tc_ws_flags;
   s.active = s.d.M > 0 && s.d.N > 0 && s.d.K > 0;
   s.plan = nullptr;
   if (!s.active || !want_tc) return B2_OK;
@@ -154,6 +158,7 @@ int check_status(b2_handle* h) {
   CK(h, cudaMemcpy(&st, h->status_dev, sizeof st, cudaMemcpyDeviceToHost));
   if (st != 0) {
     cudaMemset(h->status_dev, 0, sizeof st);
+    if (h->tc_ws_flags) cudaMemset(h->tc_ws_flags, 0, (size_t)h->sms * sizeof(unsigned int));
     return fail(h, B2_ERR_TIMEOUT, "tensor-core GEMM gave up waiting on a pipeline barrier (role %u)", st);
   }
   return B2_OK;
@@ -372,6 +377,8 @@ void free_all(b2_handle* h) {
   }
   if (h->s_copy) cudaStreamDestroy(h->s_copy);
   cudaFree(h->status_dev);
+  cudaFree(h->tc_ws);
+  cudaFree(h->tc_ws_flags);
   for (auto e : h->ev_wgrad) cudaEventDestroy(e);
   for (auto e : h->ev_dgrad) cudaEventDestroy(e);
   for (auto e : h->ev_upd) cudaEventDestroy(e);
@@ -530,6 +537,10 @@ int b2_create(const b2_config* cfg, b2_handle** out) {
     TRYCK(cudaEventCreateWithFlags(&h->ev_loss[i], cudaEventDisableTiming));
   }
   TRY(dev_alloc(h, &h->status_dev, sizeof(unsigned int)));
+  if (cfg->precision != B2_PREC_FP32 && !cfg->force_simt) {
+    TRY(dev_alloc(h, &h->tc_ws, (size_t)h->sms * TC_WS_SLOT_BYTES));
+    TRY(dev_alloc(h, &h->tc_ws_flags, (size_t)h->sms * sizeof(unsigned int)));
+  }
 
   h->ev_wgrad.assign(L, nullptr);
   h->ev_dgrad.assign(L, nullptr);
@@ -964,6 +975,13 @@ int b2_launch_counts(const b2_handle* h, long long* total, long long* tc) {
 static int gemm_common(b2_handle* h, int precision, GemmDesc& d, cudaStream_t st) {
   TcPlan* plan = nullptr;
   if (precision != B2_PREC_FP32 && !h->cfg.force_simt) {
+    if (!h->tc_ws) {  // a handle created for fp32 steps gets its tensor-core workspace on first use
+      int rc;
+      if ((rc = dev_alloc(h, &h->tc_ws, (size_t)h->sms * TC_WS_SLOT_BYTES))) return rc;
+      if ((rc = dev_alloc(h, &h->tc_ws_flags, (size_t)h->sms * sizeof(unsigned int)))) return rc;
+    }
+    d.ws = h->tc_ws;
+    d.ws_flags = h->tc_ws_flags;
     char why[128];
     plan = gemm_tc_plan_create(d, h->sms, why, sizeof why);
   }

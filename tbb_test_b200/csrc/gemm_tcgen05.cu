@@ -44,7 +44,8 @@ constexpr int SLAB_BYTES = 128;          // bytes of the contiguous dimension pe
 constexpr int KSTEP_BYTES = 32;          // bytes of K one tcgen05.mma consumes
 constexpr int KSTEPS = SLAB_BYTES / KSTEP_BYTES;
 constexpr int MAX_STAGES = 8;
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 192;       // producer warp + MMA warp + 4 epilogue warps
+constexpr int NUM_THREADS_SUB2 = 320;  // 256-row tiles: one group of 4 epilogue warps per 128-row accumulator
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
 struct TcParams {
@@ -57,6 +58,15 @@ struct TcParams {
   int split_from;        // first tile that is cut in halves
   int raster_m;          // row blocks per band of the tile order (L2 reuse, see decode_item)
   int pair;              // 1: CTA-pair kernel (cta_group::2), 256 x 256 tile per pair
+  // Stream-K: the k-blocks of all tiles form one sequence that is cut into gridDim.x
+  // equal contiguous ranges, so a tile may be computed by two or more CTAs. The CTA that
+  // holds the tile's first k-block owns it; the others store fp32 partial accumulators
+  // to their workspace slot and raise a flag.
+  int streamk;
+  int dp_tiles;           // leading tiles handed out whole, round-robin (full waves)
+  long long total_units;  // (tiles - dp_tiles) * k-blocks: the stream-K tail
+  float* ws;              // gridDim.x slots of 2 * 128 * 256 floats
+  unsigned int* ws_flags; // one per CTA, all zero between launches
   int stages;
   int tmem_cols;
   uint32_t idesc;
@@ -364,10 +374,72 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, int row, bool 
   }
 }
 
+// Piece of work of one CTA: k-blocks [kb0, kb1) of one tile (all of them unless stream-K
+// cut the tile).
+struct Work {
+  int m0, sub, n_blk, kb0, kb1;
+  long long unit0;  // position of kb0 in the stream-K sequence, -1 for a whole tile
+};
+struct WorkIter {
+  int w;
+  long long unit, end;
+};
+constexpr int WS_SLOT_FLOATS = 2 * BLOCK_M * 256;
+
+__device__ __forceinline__ long long streamk_start(const TcParams& p, int cta) {
+  return ((long long)cta * p.total_units) / (long long)gridDim.x;
+}
+__device__ __forceinline__ void work_begin(const TcParams& p, WorkIter& wi) {
+  wi.w = blockIdx.x;
+  wi.unit = streamk_start(p, blockIdx.x);
+  wi.end = streamk_start(p, blockIdx.x + 1);
+}
+// Whole tiles first (round-robin over the grid, so that the tiles in flight stay a compact
+// patch of C), then - stream-K only - this CTA's contiguous share of the k-blocks of the
+// remaining tiles.
+template <int SUB_M>
+__device__ __forceinline__ bool work_next(const TcParams& p, WorkIter& wi, Work& wk) {
+  if (p.streamk) {
+    if (wi.w < p.dp_tiles) {
+      const Item it = decode_item<SUB_M>(wi.w, 0x7fffffff, p.num_m_blocks, p.num_n_blocks, p.raster_m, p.M);
+      wk.m0 = it.m0; wk.sub = it.sub; wk.n_blk = it.n_blk; wk.kb0 = 0; wk.kb1 = p.num_k_blocks;
+      wk.unit0 = -1;
+      wi.w += gridDim.x;
+      return true;
+    }
+    if (wi.unit >= wi.end) return false;
+    const int KB = p.num_k_blocks;
+    const int tail_tile = (int)(wi.unit / KB);
+    const int tile = p.dp_tiles + tail_tile;
+    const int kb0 = (int)(wi.unit - (long long)tail_tile * KB);
+    const long long rem = wi.end - wi.unit;
+    const int kb1 = rem < (long long)(KB - kb0) ? kb0 + (int)rem : KB;
+    const Item it = decode_item<SUB_M>(tile, 0x7fffffff, p.num_m_blocks, p.num_n_blocks, p.raster_m, p.M);
+    wk.m0 = it.m0; wk.sub = it.sub; wk.n_blk = it.n_blk; wk.kb0 = kb0; wk.kb1 = kb1;
+    wk.unit0 = wi.unit;
+    wi.unit += kb1 - kb0;
+    return true;
+  }
+  if (wi.w >= p.num_items) return false;
+  const Item it = decode_item<SUB_M>(wi.w, p.split_from, p.num_m_blocks, p.num_n_blocks, p.raster_m, p.M);
+  wk.m0 = it.m0; wk.sub = it.sub; wk.n_blk = it.n_blk; wk.kb0 = 0; wk.kb1 = p.num_k_blocks;
+  wk.unit0 = -1;
+  wi.w += gridDim.x;
+  return true;
+}
+__device__ __forceinline__ unsigned int ld_acquire_u32(const unsigned int* ptr) {
+  unsigned int v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void epilogue_bar_sync(int nthreads) {
+  asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+}
+
 // ------------------------------------------------------------------------ kernel
 
 template <int SUB_M>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(SUB_M == 2 ? NUM_THREADS_SUB2 : NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                const __grid_constant__ TcParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -391,7 +463,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full_bar[a], 1);
-      mbar_init(&acc_empty_bar[a], 4);  // one arrival per epilogue warp
+      mbar_init(&acc_empty_bar[a], 4 * SUB_M);  // one arrival per epilogue warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tma_a) : "memory");
@@ -408,7 +480,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_s;
 
-  const int num_items = p.num_items;
   const uint32_t acc_cols = (uint32_t)(SUB_M * p.block_n);  // TMEM columns of one accumulator stage
   constexpr int ACC_STAGES = SUB_M == 2 ? 1 : 2;
 
@@ -418,10 +489,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int w = blockIdx.x; w < num_items && ok; w += gridDim.x) {
-        const Item it = decode_item<SUB_M>(w, p.split_from, p.num_m_blocks, p.num_n_blocks, p.raster_m, p.M);
+      WorkIter wi;
+      Work it;
+      work_begin(p, wi);
+      while (ok && work_next<SUB_M>(p, wi, it)) {
         const uint32_t a_bytes = (uint32_t)it.sub * (BLOCK_M * SLAB_BYTES);
-        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+        for (int kb = it.kb0; kb < it.kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, 1u)) { ok = false; break; }
           uint8_t* sa = smem + (size_t)stage * stage_bytes;
           uint8_t* sb = sa + p.a_stage_bytes;
@@ -468,21 +541,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       const uint32_t a_step16 = p.a_kstep >> 4, b_step16 = p.b_kstep >> 4, idesc = p.idesc;
       const uint32_t block_n = (uint32_t)p.block_n;
       const bool tf32 = p.kind_tf32 != 0;
-      for (int w = blockIdx.x; w < num_items && ok; w += gridDim.x) {
-        const Item it = decode_item<SUB_M>(w, p.split_from, p.num_m_blocks, p.num_n_blocks, p.raster_m, p.M);
+      WorkIter wi;
+      Work it;
+      work_begin(p, wi);
+      while (ok && work_next<SUB_M>(p, wi, it)) {
         if (!mbar_wait(&acc_empty_bar[acc], acc_phase ^ 1, abort_flag, p.status, 2u)) { ok = false; break; }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + (uint32_t)acc * acc_cols;
-        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+        for (int kb = it.kb0; kb < it.kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 3u)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa16 = smem16 + (uint32_t)stage * stage16;
           if (tf32)
             issue_kblock<SUB_M, true, false>(tmem_d, a_tmpl, b_tmpl, sa16, sa16 + a_stage16, a_step16, b_step16,
-                                             idesc, block_n, it.sub, kb == 0);
+                                             idesc, block_n, it.sub, kb == it.kb0);
           else
             issue_kblock<SUB_M, false, false>(tmem_d, a_tmpl, b_tmpl, sa16, sa16 + a_stage16, a_step16, b_step16,
-                                              idesc, block_n, it.sub, kb == 0);
+                                              idesc, block_n, it.sub, kb == it.kb0);
           tc_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
@@ -496,24 +571,81 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int w = blockIdx.x; w < num_items; w += gridDim.x) {
-      const Item it = decode_item<SUB_M>(w, p.split_from, p.num_m_blocks, p.num_n_blocks, p.raster_m, p.M);
+    constexpr int EPI_THREADS = 128 * SUB_M;
+    const int sub = (warp - 2) >> 2;  // each group of four epilogue warps drains one 128-row accumulator
+    WorkIter wi;
+    Work it;
+    work_begin(p, wi);
+    while (work_next<SUB_M>(p, wi, it)) {
       const int n_blk = it.n_blk;
+      const int KB = p.num_k_blocks;
+      const bool contributor = it.kb0 > 0;                 // stream-K: someone else owns this tile
+      const bool owner_partial = it.kb0 == 0 && it.kb1 < KB;  // stream-K: others finish this tile
+      const long long tile_end = it.unit0 - it.kb0 + KB;
       if (!mbar_wait(&acc_full_bar[acc], acc_phase, abort_flag, p.status, 4u)) break;
       tc_fence_after();
-#pragma unroll 1
-      for (int sub = 0; sub < it.sub; ++sub) {
+      int first_contrib = 0, last_contrib = -1;
+      if (owner_partial) {
+        // the CTAs after this one hold the rest of the tile, each as the FIRST piece of its
+        // range, so their partial sums are ready long before this CTA gets here
+        first_contrib = (int)blockIdx.x + 1;
+        last_contrib = first_contrib;
+        while (last_contrib + 1 < (int)gridDim.x && streamk_start(p, last_contrib + 1) < tile_end) ++last_contrib;
+        bool ready = true;
+        for (int c = first_contrib; c <= last_contrib && ready; ++c) {
+          const unsigned long long t0 = globaltimer();
+          unsigned int spins = 0;
+          while (ld_acquire_u32(p.ws_flags + c) == 0u) {
+            if ((++spins & 0x3F) == 0 && (*abort_flag || globaltimer() - t0 > WAIT_LIMIT_NS)) {
+              *abort_flag = 1;
+              atomicCAS(p.status, 0u, 5u);
+              ready = false;
+              break;
+            }
+          }
+        }
+        epilogue_bar_sync(EPI_THREADS);  // every epilogue thread has seen the flags
+        if (threadIdx.x == 64)
+          for (int c = first_contrib; c <= last_contrib; ++c) p.ws_flags[c] = 0u;  // consumed: re-arm
+        if (!ready) break;
+      }
+      if (sub < it.sub) {
       const int row = it.m0 + sub * BLOCK_M + q * 32 + lane;
       const bool row_ok = row < p.M;
+      const size_t ws_row = ((size_t)sub * BLOCK_M + q * 32 + lane) * (size_t)p.block_n;
       for (int c0 = 0; c0 < p.block_n; c0 += 32) {
         const int col0 = n_blk * p.block_n + c0;
         if (col0 >= p.N) break;  // uniform across the warp
         uint32_t r[32];
         tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * acc_cols +
                       (uint32_t)(sub * p.block_n + c0), r);
-        epilogue_chunk(p, row, row_ok, col0, r);
+        if (contributor) {
+          float4* dst = reinterpret_cast<float4*>(p.ws + (size_t)blockIdx.x * WS_SLOT_FLOATS + ws_row + c0);
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            dst[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                 __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+        } else {
+          for (int c = first_contrib; c <= last_contrib; ++c) {
+            const float4* src = reinterpret_cast<const float4*>(p.ws + (size_t)c * WS_SLOT_FLOATS + ws_row + c0);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float4 v = __ldcg(src + j);
+              r[4 * j] = __float_as_uint(__uint_as_float(r[4 * j]) + v.x);
+              r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + v.y);
+              r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + v.z);
+              r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + v.w);
+            }
+          }
+          epilogue_chunk(p, row, row_ok, col0, r);
+        }
       }
       }  // sub-block
+      if (contributor) {
+        __threadfence();                 // partial sums visible device-wide before the flag
+        epilogue_bar_sync(EPI_THREADS);
+        if (threadIdx.x == 64) atomicExch(p.ws_flags + blockIdx.x, 1u);
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
@@ -810,6 +942,22 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
     p.split_from = (int)T;
     if (p.sub_m == 2 && !p.pair && T > sm_count && rem > 0 && rem * 2 <= sm_count) p.split_from = (int)(T - rem);
     p.num_items = (int)(p.split_from + 2 * (T - p.split_from));
+    // Stream-K when whole tiles would leave part of the last wave idle (or there are fewer
+    // tiles than SMs) and the caller provided a workspace.
+    p.dp_tiles = (int)((T / sm_count) * sm_count);
+    p.total_units = (T - p.dp_tiles) * p.num_k_blocks;
+    // Off unless B2_TC_STREAMK=1: on the shapes of the benchmark configurations the two
+    // extra exposed epilogues of a stream-K tail (partial store, partial reload) cost about
+    // as much as the idle part of the last wave they remove; it pays for long-K shapes only.
+    const char* sk = getenv("B2_TC_STREAMK");
+    const bool allow = sk ? (sk[0] == '1') : false;
+    p.streamk = (allow && !p.pair && g.ws && g.ws_flags && T % sm_count != 0 && p.total_units >= sm_count) ? 1 : 0;
+    p.ws = g.ws;
+    p.ws_flags = g.ws_flags;
+    if (p.streamk) {
+      p.split_from = (int)T;
+      p.num_items = (int)T;
+    }
   }
   p.kind_tf32 = (eb == 4);
   p.a_mn = a_mn; p.b_mn = b_mn;
@@ -882,6 +1030,7 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
   p.epilogue = g.epilogue;
   p.alpha = g.alpha;
   plan->grid = p.num_items < sm_count ? p.num_items : sm_count;
+  if (p.streamk) plan->grid = sm_count;
   if (p.pair) {
     const int pairs = sm_count / 2;
     const int T = p.num_m_blocks * p.num_n_blocks;
@@ -927,7 +1076,7 @@ cudaError_t gemm_tc_launch(const TcPlan* plan, cudaStream_t stream, unsigned int
     return cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel, plan->map_a, plan->map_b, p);
   }
   if (p.sub_m == 2)
-    gemm_tc_kernel<2><<<plan->grid, NUM_THREADS, plan->smem, stream>>>(plan->map_a, plan->map_b, p);
+    gemm_tc_kernel<2><<<plan->grid, NUM_THREADS_SUB2, plan->smem, stream>>>(plan->map_a, plan->map_b, p);
   else
     gemm_tc_kernel<1><<<plan->grid, NUM_THREADS, plan->smem, stream>>>(plan->map_a, plan->map_b, p);
   return cudaGetLastError();

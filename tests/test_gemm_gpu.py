@@ -132,3 +132,25 @@ def test_unaligned_shape_falls_back_to_cuda_cores(dev, oracle):
         assert dev.launch_counts()[1] == before
         ref = oracle.sgemm(ta, tb, oracle.round_bf16(a), oracle.round_bf16(b))
         assert rel_fro(c, ref) <= TOL["bf16_f32out"]
+
+
+@pytest.mark.parametrize("variant", ["B2_TC_STREAMK", "B2_TC_PAIR"])
+def test_optional_tile_schedules(dev, oracle, variant, monkeypatch):
+    """The two opt-in schedules of the tensor-core kernel - stream-K on the tail wave
+    (k-blocks of a tile shared between CTAs through an fp32 workspace) and CTA pairs
+    (cta_group::2) - give the same results as the default one."""
+    from tbb_test_b200 import _capi as K
+    monkeypatch.setenv(variant, "1")
+    oracle.use_openblas()
+    try:
+        for form in FORMS:
+            for (m, n, k) in [(4096, 4096, 192), (7944, 4096, 136), (1024, 1024, 1024), (256, 512, 2048)]:
+                ta, tb, a, b = operands(oracle, form, m, n, k, 91)
+                for _ in range(2):  # twice: the workspace flags must be re-armed by the first run
+                    c = dev.sgemm_host(K.PREC_BF16, ta, tb, a, b)
+                    ref = oracle.sgemm(ta, tb, oracle.round_bf16(a), oracle.round_bf16(b))
+                    assert rel_fro(c, ref) <= TOL["bf16_f32out"], (variant, form, m, n, k)
+                    row_err = np.linalg.norm(c - ref, axis=1) / np.maximum(np.linalg.norm(ref, axis=1), 1e-30)
+                    assert row_err.max() <= 1e-4
+    finally:
+        oracle.use_builtin_gemm()
