@@ -273,7 +273,12 @@ def main():
     ap.add_argument("--precision", default="bf16", choices=["bf16", "tf32", "fp32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--comm-sms", type=int, default=-1,
+                    help="SMs the GEMM kernels leave to the collective (-1 = library default)")
+    ap.add_argument("--grad-bf16", action="store_true", help="bf16 weight gradients (configuration 5 style)")
+    ap.add_argument("--graph", action="store_true",
+                    help="replay each step as one CUDA graph (latency-bound workloads c1/c3); per-phase "
+                         "events are not available then and the roofline line uses the whole step time")
     args = ap.parse_args()
 
     rank, world = env_int("RANK", 0), env_int("WORLD_SIZE", 1)
@@ -348,7 +353,8 @@ def main():
 
     prec = {"bf16": K.PREC_BF16, "tf32": K.PREC_TF32, "fp32": K.PREC_FP32}[args.precision]
     dev = MLP(nf, batch, rank=rank, world_size=world, device=local_rank, mode=K.MODE_BASELINE, precision=prec,
-              lr=0.01, nccl_id=nccl_id, collect_timing=True)
+              lr=0.01, nccl_id=nccl_id, collect_timing=not args.graph, use_graph=args.graph,
+              comm_sms=args.comm_sms, grad_bf16=args.grad_bf16)
     b0, b1 = dev.rows
 
     # seeded synthetic data (weights seed 0, inputs seed 1, targets seed 2); every rank
@@ -386,6 +392,8 @@ def main():
     bl = b1 - b0
     gemm_flops = sum(3 * 2.0 * bl * nf[l] * nf[l + 1] for l in range(L)) * nsteps
     gemm_ms = float(phase_ms[:, [K.T_FWD, K.T_WGT_GRAD, K.T_BWD]].sum())
+    if args.graph:  # no per-phase events inside a graph: charge the whole step to the GEMMs
+        gemm_ms = step_ms
     peaks, peak_kind = measured_peaks()
     achieved_tf = gemm_flops / (gemm_ms / 1e3) / 1e12 if gemm_ms > 0 else 0.0
     peak_tf = peaks.get("bf16_tflops_sustained", 1400.0)
@@ -404,7 +412,7 @@ def main():
                         "frac": sgd_gbs / peaks["hbm_gbs"] if peaks.get("hbm_gbs") else None,
                         "note": "runs on the side stream concurrently with GEMMs"}}
     if world > 1 and per_phase["allreduce_ms"] > 0:
-        ar_bytes = n_params * 4
+        ar_bytes = n_params * (2 if args.grad_bf16 else 4)
         roofline["allreduce"] = {"busbw_gbs": ar_bytes * 2 * (world - 1) / world / (per_phase["allreduce_ms"] / 1e3) / 1e9,
                                  "note": "per-layer ncclAllReduce timed on the side stream while GEMMs run"}
 
@@ -416,7 +424,8 @@ def main():
     if not args.no_e2e:
         dev.close()
         dev = MLP(nf, batch, rank=rank, world_size=world, device=local_rank, mode=K.MODE_BASELINE,
-                  precision=prec, lr=0.01, nccl_id=None if world == 1 else e2e_id(), collect_timing=False)
+                  precision=prec, lr=0.01, nccl_id=None if world == 1 else e2e_id(), collect_timing=False,
+                  comm_sms=args.comm_sms, grad_bf16=args.grad_bf16)
         rng_w = np.random.default_rng(0)
         for l in range(L):
             dev.upload_weights(l, rng_w.uniform(-winit[1], winit[1], (nf[l + 1], nf[l])).astype(np.float32))

@@ -77,6 +77,10 @@ typedef struct {
   int collect_timing;       /* 1 = per-phase CUDA-event timing (sum_times, mlp_bench_common.h:35) */
   int use_graph;            /* 1 = replay each step as one CUDA graph */
   int force_simt;           /* 1 = never use the tensor-core kernels (debugging aid) */
+  int comm_sms;             /* SMs the persistent GEMM kernels leave free for the collective's CTAs
+                               while allreduce and GEMMs overlap (the counterpart of the threads the
+                               reference takes away from the GEMMs, mlp_bench_common.h:40-48);
+                               -1 = default: 0 for one GPU, 20 otherwise */
   float lr;                 /* SGD step (the reference hard-codes 1e-10, mlp_omp.cc:609) */
   const void* nccl_unique_id; /* B2_NCCL_ID_BYTES bytes from b2_nccl_unique_id(), shared by all
                                  ranks; NULL when world_size == 1 */
@@ -89,7 +93,7 @@ typedef struct {
 enum { B2_T_FWD = 0, B2_T_WGT_GRAD = 1, B2_T_BWD = 2, B2_T_WGT_UPDATE = 3,
        B2_T_ALLREDUCE = 4, B2_T_NUM = 5 };
 
-/* Defaults: mode BASELINE, precision FP32, world 1, allreduce/overlap/input_grad on. */
+/* Defaults: mode BASELINE, precision FP32, world 1, allreduce/overlap/input_grad on, comm_sms -1. */
 int b2_config_default(b2_config* cfg);
 
 /* Library version string and the CUDA architecture it was built for. */

@@ -71,21 +71,43 @@ __global__ void __launch_bounds__(256) loss_grad_kernel(const float* __restrict_
                                                         TO* __restrict__ dz, size_t n, int baseline,
                                                         float inv_batch, double loss_scale,
                                                         double* __restrict__ loss) {
-  double local = 0.0;
+  // fp32 partial sums per thread (a few hundred terms each), double from the block level up
+  float local = 0.f;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+  const size_t nvec = n / 4;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    float4 d = __ldg(reinterpret_cast<const float4*>(y) + i);
+    float4 g = d;
+    if (baseline) {
+      const float4 tv = __ldg(reinterpret_cast<const float4*>(t) + i);
+      d.x -= tv.x; d.y -= tv.y; d.z -= tv.z; d.w -= tv.w;
+      g.x = d.x * inv_batch; g.y = d.y * inv_batch; g.z = d.z * inv_batch; g.w = d.w * inv_batch;
+    }
+    local += 0.5f * (d.x * d.x + d.y * d.y + d.z * d.z + d.w * d.w);
+    if (sizeof(TO) == 4) {
+      reinterpret_cast<float4*>(dz)[i] = g;
+    } else {
+      __nv_bfloat162 a = __floats2bfloat162_rn(g.x, g.y);
+      __nv_bfloat162 b = __floats2bfloat162_rn(g.z, g.w);
+      uint2 o;
+      o.x = *reinterpret_cast<uint32_t*>(&a);
+      o.y = *reinterpret_cast<uint32_t*>(&b);
+      reinterpret_cast<uint2*>(dz)[i] = o;
+    }
+  }
+  for (size_t i = nvec * 4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
     float d = y[i];
     float g = d;
     if (baseline) {
       d -= t[i];
       g = d * inv_batch;
     }
-    local += 0.5 * (double)d * (double)d;
+    local += 0.5f * d * d;
     if (sizeof(TO) == 4) reinterpret_cast<float*>(dz)[i] = g;
     else reinterpret_cast<__nv_bfloat16*>(dz)[i] = __float2bfloat16_rn(g);
   }
   __shared__ double red[256];
-  red[threadIdx.x] = local;
+  red[threadIdx.x] = (double)local;
   __syncthreads();
   for (int s = 128; s > 0; s >>= 1) {
     if (threadIdx.x < s) red[threadIdx.x] += red[threadIdx.x + s];
@@ -174,7 +196,7 @@ cudaError_t loss_grad_launch(const float* y, const float* target, void* dz, int 
                              int baseline, float inv_batch, double loss_scale, double* loss,
                              cudaStream_t s) {
   if (n == 0) return cudaSuccess;
-  int grid = grid_for(n, device_sms(), 4);
+  int grid = grid_for(n / 4 + 1, device_sms(), 8);
   if (dz_type == T_BF16)
     loss_grad_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(y, target, (__nv_bfloat16*)dz, n, baseline,
                                                          inv_batch, loss_scale, loss);

@@ -44,9 +44,16 @@ struct b2_handle {
   b2_config cfg;
   std::vector<int> nf;
   int L = 0, b0 = 0, b1 = 0, bl = 0, sms = 148;
+  int gemm_sms = 148;  // SMs the persistent GEMM kernels of the step occupy (sms - comm_sms)
   int op_type = T_F32;    // element type of GEMM operands held on the device
   int grad_type = T_F32;  // element type of dW
   cudaStream_t s_main = nullptr, s_comm = nullptr;
+  // Weight-gradient GEMMs run on a stream of their own next to the input-gradient chain:
+  // both are persistent kernels, so the CTAs of one start on the SMs the other's last,
+  // partial wave leaves idle instead of waiting for the whole kernel to drain.
+  cudaStream_t s_wg = nullptr;
+  cudaEvent_t ev_dz_last = nullptr;
+  bool wg_stream = false;
   std::vector<float*> w;
   std::vector<__nv_bfloat16*> w16;
   std::vector<void*> dw, act, dz;
@@ -131,7 +138,7 @@ int make_site(b2_handle* h, Site& s, bool want_tc) {
   s.plan = nullptr;
   if (!s.active || !want_tc) return B2_OK;
   char why[128];
-  s.plan = gemm_tc_plan_create(s.d, h->sms, why, sizeof why);
+  s.plan = gemm_tc_plan_create(s.d, h->gemm_sms, why, sizeof why);
   return B2_OK;  // a refused plan silently means the CUDA-core kernel serves this site
 }
 
@@ -285,7 +292,8 @@ int enqueue_step(b2_handle* h, bool timed, int slot = 0) {
   double* loss_acc = h->loss_dev + slot;
   const float* target = slot ? h->target_alt : h->target;
   const bool overlap = h->cfg.overlap != 0;
-  cudaStream_t sm = h->s_main, sc = overlap ? h->s_comm : h->s_main;
+  const bool wg = overlap && h->wg_stream;
+  cudaStream_t sm = h->s_main, sc = overlap ? h->s_comm : h->s_main, sw = wg ? h->s_wg : h->s_main;
   int rc;
   CK(h, cudaMemsetAsync(loss_acc, 0, sizeof(double), sm));
   for (int l = 0; l < L; ++l) {
@@ -303,17 +311,20 @@ int enqueue_step(b2_handle* h, bool timed, int slot = 0) {
     CK(h, loss_grad_launch(h->y, target, h->dz[L - 1], h->op_type, n, baseline ? 1 : 0,
                            1.0f / (float)h->cfg.batch, baseline ? 1.0 / (double)h->cfg.batch : 1.0, loss_acc, sm));
     if (n) ++h->launches;
+    if (wg) CK(h, cudaEventRecord(h->ev_dz_last, sm));
   }
   for (int l = L - 1; l >= 0; --l) {
-    if (timed) CK(h, cudaEventRecord(phase_ev(h, l, B2_T_WGT_GRAD, 0), sm));
+    // wgrad(l) needs dZ[l]: the output gradient for the last layer, dgrad(l+1) otherwise
+    if (wg) CK(h, cudaStreamWaitEvent(sw, l == L - 1 ? h->ev_dz_last : h->ev_dgrad[l + 1], 0));
+    if (timed) CK(h, cudaEventRecord(phase_ev(h, l, B2_T_WGT_GRAD, 0), sw));
     if (h->wgrad[l].active) {
-      if ((rc = run_site(h, (l == 0 && slot) ? h->wgrad0_alt : h->wgrad[l], sm))) return rc;
+      if ((rc = run_site(h, (l == 0 && slot) ? h->wgrad0_alt : h->wgrad[l], sw))) return rc;
     } else {  // a rank without batch rows contributes a zero gradient
-      CK(h, cudaMemsetAsync(h->dw[l], 0, (size_t)h->nf[l + 1] * h->nf[l] * esize(h->grad_type), sm));
+      CK(h, cudaMemsetAsync(h->dw[l], 0, (size_t)h->nf[l + 1] * h->nf[l] * esize(h->grad_type), sw));
     }
-    if (timed) CK(h, cudaEventRecord(phase_ev(h, l, B2_T_WGT_GRAD, 1), sm));
+    if (timed) CK(h, cudaEventRecord(phase_ev(h, l, B2_T_WGT_GRAD, 1), sw));
     if (overlap) {
-      CK(h, cudaEventRecord(h->ev_wgrad[l], sm));
+      CK(h, cudaEventRecord(h->ev_wgrad[l], sw));
       CK(h, cudaStreamWaitEvent(sc, h->ev_wgrad[l], 0));
     }
     if ((rc = layer_update(h, l, sc, timed))) return rc;
@@ -330,6 +341,9 @@ int enqueue_step(b2_handle* h, bool timed, int slot = 0) {
       h->upd_pending[l] = 1;
     }
   }
+  // the step's inputs (read by wgrad(0)) are free, and the step is over on the main stream,
+  // only once the last weight-gradient GEMM is done
+  if (wg) CK(h, cudaStreamWaitEvent(sm, h->ev_wgrad[0], 0));
   return B2_OK;
 }
 
@@ -348,6 +362,11 @@ void free_all(b2_handle* h) {
   if (h->s_main) cudaStreamSynchronize(h->s_main);
   if (h->s_comm) cudaStreamSynchronize(h->s_comm);
   if (h->s_copy) cudaStreamSynchronize(h->s_copy);
+  if (h->s_wg) {
+    cudaStreamSynchronize(h->s_wg);
+    cudaStreamDestroy(h->s_wg);
+  }
+  if (h->ev_dz_last) cudaEventDestroy(h->ev_dz_last);
   if (h->comm && nccl_api().ok) nccl_api().CommDestroy(h->comm);
   if (h->graph_exec) cudaGraphExecDestroy(h->graph_exec);
   for (auto& s : h->fwd) gemm_tc_plan_destroy(s.plan);
@@ -415,6 +434,7 @@ int b2_config_default(b2_config* c) {
   c->allreduce = 1;
   c->overlap = 1;
   c->input_grad = 1;
+  c->comm_sms = -1;
   c->lr = 0.01f;
   return B2_OK;
 }
@@ -495,9 +515,35 @@ int b2_create(const b2_config* cfg, b2_handle** out) {
     TRY(fail(h, B2_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only", cfg->device,
              prop.major, prop.minor));
   h->sms = prop.multiProcessorCount;
+  {
+    const bool comm = cfg->world_size > 1 && cfg->allreduce && cfg->overlap;
+    int reserve = cfg->comm_sms < 0 ? (comm ? 20 : 0) : cfg->comm_sms;
+    if (reserve > h->sms / 2) reserve = h->sms / 2;
+    h->gemm_sms = h->sms - reserve;
+    h->cfg.comm_sms = reserve;
+    // keep the collective inside the SMs set aside for it (a setting the caller made wins)
+    if (comm && reserve > 0) {
+      char v[16];
+      snprintf(v, sizeof v, "%d", reserve);
+      setenv("NCCL_MAX_CTAS", v, 0);
+    }
+  }
   TRYCK(cudaStreamCreateWithFlags(&h->s_main, cudaStreamNonBlocking));
-  TRYCK(cudaStreamCreateWithFlags(&h->s_comm, cudaStreamNonBlocking));
+  {
+    // the side stream's kernels (collective, SGD) should take free SMs before the next GEMM does
+    int lo = 0, hi = 0;
+    TRYCK(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+    TRYCK(cudaStreamCreateWithPriority(&h->s_comm, cudaStreamNonBlocking, hi));
+  }
 
+  TRYCK(cudaStreamCreateWithFlags(&h->s_wg, cudaStreamNonBlocking));
+  TRYCK(cudaEventCreateWithFlags(&h->ev_dz_last, cudaEventDisableTiming));
+  {
+    // off when the stream-K schedule is requested: its workspace is shared by the handle's GEMMs
+    const char* e = getenv("B2_WGRAD_STREAM");
+    const char* sk = getenv("B2_TC_STREAMK");
+    h->wg_stream = (e ? e[0] != '0' : true) && !(sk && sk[0] == '1');
+  }
   const int L = h->L;
   const size_t bl = (size_t)h->bl;
   h->w.assign(L, nullptr);
@@ -684,6 +730,7 @@ int b2_sync(b2_handle* h) {
   ENTER(h);
   CK(h, cudaStreamSynchronize(h->s_main));
   CK(h, cudaStreamSynchronize(h->s_comm));
+  CK(h, cudaStreamSynchronize(h->s_wg));
   return check_status(h);
 }
 

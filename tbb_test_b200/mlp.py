@@ -30,7 +30,7 @@ def nccl_unique_id():
 class MLP:
     def __init__(self, nfeatures, batch, *, rank=0, world_size=1, device=0, mode=K.MODE_BASELINE,
                  precision=K.PREC_FP32, grad_bf16=False, allreduce=True, overlap=True, input_grad=True,
-                 collect_timing=False, use_graph=False, force_simt=False, lr=0.01, nccl_id=None):
+                 collect_timing=False, use_graph=False, force_simt=False, lr=0.01, nccl_id=None, comm_sms=-1):
         self.lib = K.lib()
         self.nf = [int(f) for f in nfeatures]
         self.L = len(self.nf) - 1
@@ -47,6 +47,7 @@ class MLP:
         cfg.allreduce, cfg.overlap, cfg.input_grad = int(allreduce), int(overlap), int(input_grad)
         cfg.collect_timing, cfg.use_graph, cfg.force_simt = int(collect_timing), int(use_graph), int(force_simt)
         cfg.lr = lr
+        cfg.comm_sms = comm_sms
         self._id = None
         if nccl_id is not None:
             self._id = C.create_string_buffer(bytes(nccl_id), K.NCCL_ID_BYTES)

@@ -299,3 +299,31 @@ def test_pipelined_host_fed_steps_equal_the_blocking_call(native, oracle, prec):
     a.close()
     b.close()
     orc.close()
+
+
+def test_bf16_gradients_mode(native, oracle):
+    """Configuration-5 style: weight gradients produced, summed and read by SGD in bf16
+    (fp32 master weights). One step against the oracle that rounds the same way; the
+    gradient itself differs by bf16 rounding only."""
+    from tbb_test_b200 import _capi as K
+    from tbb_test_b200.mlp import MLP
+    nf, batch = [256, 512, 256], 256
+    ws, x, t = make_problem(oracle, nf, batch)
+    dev = MLP(nf, batch, precision=K.PREC_BF16, grad_bf16=True, lr=0.01)
+    orc = oracle.Oracle(nf, batch, mode=oracle.MODE_BASELINE, rounding=oracle.ROUND_BF16, grad_bf16=True, lr=0.01)
+    for l in range(2):
+        dev.upload_weights(l, ws[l])
+        orc.set_weights(l, ws[l])
+    dev.upload_input(x)
+    dev.upload_target(t)
+    orc.set_input(x)
+    orc.set_target(t)
+    dev.step(1)
+    orc.step(1)
+    for l in range(2):
+        g = dev.weight_grad(l)
+        assert np.array_equal(g, oracle.round_bf16(g)), "gradient buffer is not bf16-valued"
+        assert rel_fro(g, orc.weight_grad(l)) <= 5e-3
+        assert rel_fro(dev.weights(l) - ws[l], orc.weights(l) - ws[l]) <= 5e-3
+    dev.close()
+    orc.close()
