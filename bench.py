@@ -275,6 +275,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--comm-sms", type=int, default=-1,
                     help="SMs the GEMM kernels leave to the collective (-1 = library default)")
+    ap.add_argument("--bucket-mb", type=int, default=-1,
+                    help="gradient allreduce granularity in MiB (0 = per layer, -1 = library default)")
     ap.add_argument("--grad-bf16", action="store_true", help="bf16 weight gradients (configuration 5 style)")
     ap.add_argument("--graph", action="store_true",
                     help="replay each step as one CUDA graph (latency-bound workloads c1/c3); per-phase "
@@ -354,7 +356,7 @@ def main():
     prec = {"bf16": K.PREC_BF16, "tf32": K.PREC_TF32, "fp32": K.PREC_FP32}[args.precision]
     dev = MLP(nf, batch, rank=rank, world_size=world, device=local_rank, mode=K.MODE_BASELINE, precision=prec,
               lr=0.01, nccl_id=nccl_id, collect_timing=not args.graph, use_graph=args.graph,
-              comm_sms=args.comm_sms, grad_bf16=args.grad_bf16)
+              comm_sms=args.comm_sms, grad_bf16=args.grad_bf16, ar_bucket_mb=args.bucket_mb)
     b0, b1 = dev.rows
 
     # seeded synthetic data (weights seed 0, inputs seed 1, targets seed 2); every rank
@@ -425,7 +427,7 @@ def main():
         dev.close()
         dev = MLP(nf, batch, rank=rank, world_size=world, device=local_rank, mode=K.MODE_BASELINE,
                   precision=prec, lr=0.01, nccl_id=None if world == 1 else e2e_id(), collect_timing=False,
-                  comm_sms=args.comm_sms, grad_bf16=args.grad_bf16)
+                  comm_sms=args.comm_sms, grad_bf16=args.grad_bf16, ar_bucket_mb=args.bucket_mb)
         rng_w = np.random.default_rng(0)
         for l in range(L):
             dev.upload_weights(l, rng_w.uniform(-winit[1], winit[1], (nf[l + 1], nf[l])).astype(np.float32))

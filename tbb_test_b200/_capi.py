@@ -28,7 +28,7 @@ class Config(C.Structure):
         ("nlayers", C.c_int), ("nfeatures", C.POINTER(C.c_int)), ("batch", C.c_int), ("rank", C.c_int),
         ("world_size", C.c_int), ("device", C.c_int), ("mode", C.c_int), ("precision", C.c_int),
         ("grad_bf16", C.c_int), ("allreduce", C.c_int), ("overlap", C.c_int), ("input_grad", C.c_int),
-        ("collect_timing", C.c_int), ("use_graph", C.c_int), ("force_simt", C.c_int), ("comm_sms", C.c_int), ("lr", C.c_float),
+        ("collect_timing", C.c_int), ("use_graph", C.c_int), ("force_simt", C.c_int), ("comm_sms", C.c_int), ("ar_bucket_mb", C.c_int), ("lr", C.c_float),
         ("nccl_unique_id", C.c_void_p),
     ]
 

@@ -57,6 +57,12 @@ struct b2_handle {
   std::vector<float*> w;
   std::vector<__nv_bfloat16*> w16;
   std::vector<void*> dw, act, dz;
+  // All weight gradients live in one slab, last layer first (the order backward produces
+  // them), so that consecutive layers can be summed by one collective call ("bucket").
+  void* dw_slab = nullptr;
+  std::vector<size_t> dw_off;       // element offset of dw[l] in the slab
+  std::vector<int> bucket_low;      // for layer l: lowest layer index of its bucket
+  std::vector<int> bucket_high;     // for layer l: highest layer index of its bucket
   float* y = nullptr;
   float* target = nullptr;
   void* dinput = nullptr;
@@ -276,6 +282,19 @@ int layer_update(b2_handle* h, int l, cudaStream_t st, bool timed) {
   return B2_OK;
 }
 
+// Sum of the gradients of layers [low, high] (contiguous in the slab, `high` first) over all ranks.
+int bucket_allreduce(b2_handle* h, int low, int high, cudaStream_t st, bool timed) {
+  if (!(h->cfg.world_size > 1 && h->cfg.allreduce)) return B2_OK;
+  const size_t begin = h->dw_off[high];
+  const size_t end = h->dw_off[low] + (size_t)h->nf[low + 1] * h->nf[low];
+  char* base = static_cast<char*>(h->dw_slab) + begin * esize(h->grad_type);
+  if (timed) CK(h, cudaEventRecord(phase_ev(h, low, B2_T_ALLREDUCE, 0), st));
+  NCK(h, nccl_api().AllReduce(base, base, end - begin, h->grad_type == T_BF16 ? ncclBfloat16 : ncclFloat32, ncclSum,
+                              h->comm, st));
+  if (timed) CK(h, cudaEventRecord(phase_ev(h, low, B2_T_ALLREDUCE, 1), st));
+  return B2_OK;
+}
+
 int layer_sgd(b2_handle* h, int l, cudaStream_t st, bool timed) {
   const size_t n = (size_t)h->nf[l + 1] * h->nf[l];
   if (timed) CK(h, cudaEventRecord(phase_ev(h, l, B2_T_WGT_UPDATE, 0), st));
@@ -323,22 +342,27 @@ int enqueue_step(b2_handle* h, bool timed, int slot = 0) {
       CK(h, cudaMemsetAsync(h->dw[l], 0, (size_t)h->nf[l + 1] * h->nf[l] * esize(h->grad_type), sw));
     }
     if (timed) CK(h, cudaEventRecord(phase_ev(h, l, B2_T_WGT_GRAD, 1), sw));
+    const bool closes_bucket = (h->bucket_low[l] == l);
     if (overlap) {
       CK(h, cudaEventRecord(h->ev_wgrad[l], sw));
-      CK(h, cudaStreamWaitEvent(sc, h->ev_wgrad[l], 0));
+      if (closes_bucket) CK(h, cudaStreamWaitEvent(sc, h->ev_wgrad[l], 0));  // in-order stream: all of the bucket
     }
-    if ((rc = layer_update(h, l, sc, timed))) return rc;
+    if (closes_bucket && (rc = bucket_allreduce(h, l, h->bucket_high[l], sc, timed))) return rc;
     if (timed) CK(h, cudaEventRecord(phase_ev(h, l, B2_T_BWD, 0), sm));
     if ((rc = run_site(h, h->dgrad[l], sm))) return rc;
     if (timed) CK(h, cudaEventRecord(phase_ev(h, l, B2_T_BWD, 1), sm));
-    if (overlap) {
-      CK(h, cudaEventRecord(h->ev_dgrad[l], sm));
-      CK(h, cudaStreamWaitEvent(sc, h->ev_dgrad[l], 0));
-    }
-    if ((rc = layer_sgd(h, l, sc, timed))) return rc;
-    if (overlap) {
-      CK(h, cudaEventRecord(h->ev_upd[l], sc));
-      h->upd_pending[l] = 1;
+    if (overlap) CK(h, cudaEventRecord(h->ev_dgrad[l], sm));
+    if (closes_bucket) {
+      // SGD of every layer of the bucket: after the sum, and after dgrad(l) - the last reader of
+      // the bucket's old weights on the in-order main stream
+      if (overlap) CK(h, cudaStreamWaitEvent(sc, h->ev_dgrad[l], 0));
+      for (int k = h->bucket_high[l]; k >= l; --k) {
+        if ((rc = layer_sgd(h, k, sc, timed))) return rc;
+        if (overlap) {
+          CK(h, cudaEventRecord(h->ev_upd[k], sc));
+          h->upd_pending[k] = 1;
+        }
+      }
     }
   }
   // the step's inputs (read by wgrad(0)) are free, and the step is over on the main stream,
@@ -374,7 +398,7 @@ void free_all(b2_handle* h) {
   for (auto& s : h->dgrad) gemm_tc_plan_destroy(s.plan);
   for (auto p : h->w) cudaFree(p);
   for (auto p : h->w16) cudaFree(p);
-  for (auto p : h->dw) cudaFree(p);
+  cudaFree(h->dw_slab);
   for (auto p : h->act) cudaFree(p);
   for (auto p : h->dz) cudaFree(p);
   cudaFree(h->y);
@@ -435,6 +459,7 @@ int b2_config_default(b2_config* c) {
   c->overlap = 1;
   c->input_grad = 1;
   c->comm_sms = -1;
+  c->ar_bucket_mb = -1;
   c->lr = 0.01f;
   return B2_OK;
 }
@@ -556,12 +581,48 @@ int b2_create(const b2_config* cfg, b2_handle** out) {
     const size_t nw = (size_t)h->nf[l + 1] * h->nf[l];
     TRY(dev_alloc(h, &h->w[l], nw * 4));
     if (h->op_type == T_BF16) TRY(dev_alloc(h, &h->w16[l], nw * 2));
-    TRY(dev_alloc(h, &h->dw[l], nw * esize(h->grad_type)));
+
     TRY(dev_alloc(h, &h->dz[l], bl * h->nf[l + 1] * esize(h->op_type)));
     TRY(dev_alloc(h, &h->act[l], bl * h->nf[l] * esize(h->op_type)));
     if (nw > max_elems) max_elems = nw;
     if (bl * h->nf[l] > max_elems) max_elems = bl * h->nf[l];
     if (bl * h->nf[l + 1] > max_elems) max_elems = bl * h->nf[l + 1];
+  }
+  {
+    // gradient slab, last layer first; every layer starts on a 256-byte boundary
+    h->dw_off.assign(L, 0);
+    const size_t es = esize(h->grad_type), align_elems = 256 / es;
+    size_t total = 0, total_bytes_all = 0;
+    for (int l = L - 1; l >= 0; --l) {
+      h->dw_off[l] = total;
+      const size_t nw = (size_t)h->nf[l + 1] * h->nf[l];
+      total += (nw + align_elems - 1) / align_elems * align_elems;
+      total_bytes_all += nw * es;
+    }
+    TRY(dev_alloc(h, &h->dw_slab, total * es));
+    for (int l = 0; l < L; ++l) h->dw[l] = static_cast<char*>(h->dw_slab) + h->dw_off[l] * es;
+    // buckets: consecutive layers until about a quarter of all gradient bytes (at least 4 MiB);
+    // one layer per bucket when there is nothing to sum or the caller asks for it
+    const bool multi = cfg->world_size > 1 && cfg->allreduce;
+    size_t target = total_bytes_all / 4;
+    if (target < ((size_t)4 << 20)) target = (size_t)4 << 20;
+    if (cfg->ar_bucket_mb == 0 || !multi) target = 0;
+    if (cfg->ar_bucket_mb > 0) target = (size_t)cfg->ar_bucket_mb << 20;
+    h->bucket_low.assign(L, 0);
+    h->bucket_high.assign(L, 0);
+    int high = L - 1;
+    size_t acc = 0;
+    for (int l = L - 1; l >= 0; --l) {
+      acc += (size_t)h->nf[l + 1] * h->nf[l] * es;
+      if (acc >= target || l == 0) {
+        for (int k = high; k >= l; --k) {
+          h->bucket_low[k] = l;
+          h->bucket_high[k] = high;
+        }
+        high = l - 1;
+        acc = 0;
+      }
+    }
   }
   TRY(dev_alloc(h, &h->y, bl * h->nf[L] * 4));
   TRY(dev_alloc(h, &h->target, bl * h->nf[L] * 4));

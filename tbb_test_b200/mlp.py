@@ -30,7 +30,7 @@ def nccl_unique_id():
 class MLP:
     def __init__(self, nfeatures, batch, *, rank=0, world_size=1, device=0, mode=K.MODE_BASELINE,
                  precision=K.PREC_FP32, grad_bf16=False, allreduce=True, overlap=True, input_grad=True,
-                 collect_timing=False, use_graph=False, force_simt=False, lr=0.01, nccl_id=None, comm_sms=-1):
+                 collect_timing=False, use_graph=False, force_simt=False, lr=0.01, nccl_id=None, comm_sms=-1, ar_bucket_mb=-1):
         self.lib = K.lib()
         self.nf = [int(f) for f in nfeatures]
         self.L = len(self.nf) - 1
@@ -48,6 +48,7 @@ class MLP:
         cfg.collect_timing, cfg.use_graph, cfg.force_simt = int(collect_timing), int(use_graph), int(force_simt)
         cfg.lr = lr
         cfg.comm_sms = comm_sms
+        cfg.ar_bucket_mb = ar_bucket_mb
         self._id = None
         if nccl_id is not None:
             self._id = C.create_string_buffer(bytes(nccl_id), K.NCCL_ID_BYTES)

@@ -51,9 +51,11 @@ def main():
     ws, x, t = make_problem(O, nf, batch)
     for prec, rounding, tol in ((K.PREC_FP32, O.ROUND_NONE, dict(state=2e-5, grad=2e-5)),
                                 (K.PREC_BF16, O.ROUND_BF16, dict(state=5e-3, grad=1e-1))):
-        for overlap in (True, False):
+        # two-stream schedule with the default gradient buckets, with one collective per layer,
+        # and the serial schedule
+        for overlap, bucket in ((True, -1), (True, 0), (False, -1)):
             dev = MLP(nf, batch, rank=rank, world_size=world, device=local, precision=prec, lr=0.01,
-                      nccl_id=fresh_id(), overlap=overlap)
+                      nccl_id=fresh_id(), overlap=overlap, ar_bucket_mb=bucket)
             orc = O.Oracle(nf, batch, nranks=world, mode=O.MODE_BASELINE, rounding=rounding, lr=0.01)
             for l in range(3):
                 dev.upload_weights(l, ws[l])
