@@ -416,7 +416,43 @@ def main():
     if world > 1 and per_phase["allreduce_ms"] > 0:
         ar_bytes = n_params * (2 if args.grad_bf16 else 4)
         roofline["allreduce"] = {"busbw_gbs": ar_bytes * 2 * (world - 1) / world / (per_phase["allreduce_ms"] / 1e3) / 1e9,
-                                 "note": "per-layer ncclAllReduce timed on the side stream while GEMMs run"}
+                                 "note": "gradient ncclAllReduce calls timed on the side stream while GEMMs run"}
+        # How much of the allreduce hides behind compute: 1 - (t_step - t_step,no allreduce) / t_allreduce,alone
+        # (the reference's NO_ALL_REDUCE build gives the middle term, mlp_omp.cc:21). The buckets are
+        # those of the library's default rule: consecutive layers up to a quarter of all gradient bytes.
+        es = 2 if args.grad_bf16 else 4
+        sizes = [nf[l] * nf[l + 1] * es for l in range(L - 1, -1, -1)]
+        target = max(sum(sizes) // 4, 4 << 20) if args.bucket_mb < 0 else args.bucket_mb << 20
+        buckets, acc = [], 0
+        for i, b in enumerate(sizes):
+            acc += b
+            if acc >= target or i == len(sizes) - 1:
+                buckets.append(acc)
+                acc = 0
+        t_alone = 0.0
+        for b in buckets:
+            barrier()
+            ms, _ = dev.allreduce_bench(b // es, K.DTYPE_BF16 if args.grad_bf16 else K.DTYPE_F32, 3, 10)
+            t_alone += max_over_ranks(ms)
+        noar = MLP(nf, batch, rank=rank, world_size=world, device=local_rank, mode=K.MODE_BASELINE, precision=prec,
+                   lr=0.01, allreduce=False, grad_bf16=args.grad_bf16)
+        rng_n = np.random.default_rng(0)
+        for l in range(L):
+            noar.upload_weights(l, rng_n.uniform(-winit[1], winit[1], (nf[l + 1], nf[l])).astype(np.float32))
+        noar.upload_input(x_host)
+        noar.upload_target(t_host)
+        noar.step(warmup)
+        noar.reset_timing()
+        barrier()
+        noar.step(args.steps)
+        barrier()
+        _, ms_noar, n_noar = noar.timing()
+        noar.close()
+        t_noar = max_over_ranks(ms_noar / max(n_noar, 1))
+        roofline["allreduce"].update({
+            "alone_ms_per_step": t_alone, "buckets_bytes": buckets, "step_ms_without_allreduce": t_noar,
+            "hidden_fraction": 1.0 - (ms_per_step - t_noar) / t_alone if t_alone > 0 else None,
+            "busbw_alone_gbs": sum(buckets) * 2 * (world - 1) / world / (t_alone / 1e3) / 1e9 if t_alone > 0 else None})
 
     # ---- end to end through the host-facing call --------------------------------
     # Every step: this step's inputs and targets are copied from pinned host memory

@@ -223,6 +223,11 @@ int b2_allreduce_bench(b2_handle* h, size_t count, int dtype, int warmup, int it
  * (mlp_bench_common.cc:38-150). Pointers may be NULL. */
 int b2_get_timing(b2_handle* h, double* phase_ms, double* step_ms, long long* steps);
 int b2_reset_timing(b2_handle* h);
+/* Chrome-trace ("trace event") JSON of the most recent b2_step call made with collect_timing:
+ * one complete event per layer and phase, pid = rank, tid = stream (0 main, 1 weight-gradient
+ * stream, 2 side stream). Same idea as the reference's COLLECT_TRACE dump (mlp_tbb.cc:82-108,
+ * 1378-1392), with GPUs for sockets and streams for threads. */
+int b2_write_trace(b2_handle* h, const char* path);
 
 /* Number of kernels of this library launched on the handle since creation, and
  * how many of them were tensor-core (tcgen05) GEMMs. */

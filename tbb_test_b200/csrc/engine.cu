@@ -92,6 +92,11 @@ struct b2_handle {
   long long async_issued = 0, async_waited = 0;
   ncclComm_t comm = nullptr;
   std::vector<double> phase_ms;
+  struct TraceEvent {
+    int step, layer, phase;
+    float start_ms, dur_ms;  // relative to the start of the b2_step call
+  };
+  std::vector<TraceEvent> trace;  // phases of the most recent timed b2_step call
   double step_ms = 0;
   long long steps = 0, launches = 0, tc_launches = 0;
   cudaGraphExec_t graph_exec = nullptr;
@@ -874,15 +879,19 @@ int b2_step(b2_handle* h, int iters) {
   h->step_ms += ms;
   h->steps += iters;
   if (timed) {
+    h->trace.clear();
     for (int it = 0; it < iters; ++it) {
       h->ev_iter = it;
       for (int l = 0; l < h->L; ++l)
         for (int ph = 0; ph < B2_T_NUM; ++ph) {
-          float pm = 0.f;
-          if (cudaEventElapsedTime(&pm, phase_ev(h, l, ph, 0), phase_ev(h, l, ph, 1)) == cudaSuccess)
+          float pm = 0.f, t0 = 0.f;
+          if (cudaEventElapsedTime(&pm, phase_ev(h, l, ph, 0), phase_ev(h, l, ph, 1)) == cudaSuccess) {
             h->phase_ms[(size_t)l * B2_T_NUM + ph] += pm;
-          else
+            if (cudaEventElapsedTime(&t0, h->ev_t0, phase_ev(h, l, ph, 0)) == cudaSuccess)
+              h->trace.push_back({it, l, ph, t0, pm});
+          } else {
             cudaGetLastError();  // phase not recorded in this configuration (e.g. no allreduce)
+          }
         }
     }
     for (auto ev : h->ev_phase) cudaEventDestroy(ev);
@@ -1062,6 +1071,27 @@ int b2_get_timing(b2_handle* h, double* phase_ms, double* step_ms, long long* st
   if (phase_ms) memcpy(phase_ms, h->phase_ms.data(), h->phase_ms.size() * sizeof(double));
   if (step_ms) *step_ms = h->step_ms;
   if (steps) *steps = h->steps;
+  return B2_OK;
+}
+
+int b2_write_trace(b2_handle* h, const char* path) {
+  if (!h || !path) return fail(h, B2_ERR_INVALID, "null argument");
+  if (h->trace.empty()) return fail(h, B2_ERR_STATE, "no timed step recorded (needs collect_timing = 1)");
+  FILE* f = fopen(path, "w");
+  if (!f) return fail(h, B2_ERR_INVALID, "cannot open %s", path);
+  static const char* names[B2_T_NUM] = {"fwd", "wgt_grad", "bwd", "wgt_update", "allreduce"};
+  // one "thread" per stream: main (fwd, bwd), weight-gradient stream, side stream (allreduce, update)
+  static const int tid[B2_T_NUM] = {0, 1, 0, 2, 2};
+  fprintf(f, "[\n");
+  for (size_t i = 0; i < h->trace.size(); ++i) {
+    const auto& e = h->trace[i];
+    fprintf(f, "{\"name\": \"%s %d\", \"ph\": \"X\", \"pid\": %d, \"tid\": %d, \"ts\": %.3f, \"dur\": %.3f, "
+               "\"args\": {\"step\": %d}}%s\n",
+            names[e.phase], e.layer, h->cfg.rank, tid[e.phase], e.start_ms * 1e3, e.dur_ms * 1e3, e.step,
+            i + 1 < h->trace.size() ? "," : "");
+  }
+  fprintf(f, "]\n");
+  fclose(f);
   return B2_OK;
 }
 

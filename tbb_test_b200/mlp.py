@@ -193,6 +193,9 @@ class MLP:
         self._ck(self.lib.b2_get_timing(self._h, ph, C.byref(ms), C.byref(n)))
         return np.array(ph[:]).reshape(self.L, K.T_NUM), ms.value, n.value
 
+    def write_trace(self, path):
+        self._ck(self.lib.b2_write_trace(self._h, str(path).encode()))
+
     def reset_timing(self):
         self._ck(self.lib.b2_reset_timing(self._h))
 

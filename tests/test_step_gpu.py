@@ -327,3 +327,30 @@ def test_bf16_gradients_mode(native, oracle):
         assert rel_fro(dev.weights(l) - ws[l], orc.weights(l) - ws[l]) <= 5e-3
     dev.close()
     orc.close()
+
+
+def test_chrome_trace_of_a_timed_step(native, oracle, tmp_path):
+    import json
+    from tbb_test_b200 import _capi as K
+    from tbb_test_b200.mlp import MLP
+    nf, batch = [128, 256, 128], 128
+    ws, x, t = make_problem(oracle, nf, batch)
+    dev = MLP(nf, batch, collect_timing=True)
+    for l in range(2):
+        dev.upload_weights(l, ws[l])
+    dev.upload_input(x)
+    dev.upload_target(t)
+    dev.step(2)
+    path = tmp_path / "trace.json"
+    dev.write_trace(path)
+    ev = json.loads(path.read_text())
+    names = {e["name"] for e in ev}
+    assert {"fwd 0", "fwd 1", "wgt_grad 0", "wgt_grad 1", "bwd 0", "bwd 1", "wgt_update 0", "wgt_update 1"} <= names
+    assert all(e["ph"] == "X" and e["dur"] >= 0 and e["ts"] >= 0 for e in ev)
+    assert {e["args"]["step"] for e in ev} == {0, 1}
+    phases, total, steps = dev.timing()
+    assert steps == 2 and total > 0 and phases[:, K.T_FWD].sum() > 0
+    plain = MLP(nf, batch)
+    assert plain.lib.b2_write_trace(plain._h, str(path).encode()) == K.ERR_STATE
+    plain.close()
+    dev.close()
