@@ -222,6 +222,11 @@ int b2_allreduce_bench(b2_handle* h, size_t count, int dtype, int warmup, int it
  * *step_ms / *steps for whole steps (always collected). Feeds report_timing
  * (mlp_bench_common.cc:38-150). Pointers may be NULL. */
 int b2_get_timing(b2_handle* h, double* phase_ms, double* step_ms, long long* steps);
+/* Milliseconds since the last reset during which at least one GEMM of the steps was running
+ * (needs collect_timing). The weight-gradient GEMMs run next to the input-gradient GEMMs on a
+ * second stream, so the per-phase sums of b2_get_timing count overlapped time twice; a GEMM
+ * rate is flops / this number. */
+int b2_get_gemm_busy_ms(b2_handle* h, double* ms);
 int b2_reset_timing(b2_handle* h);
 /* Chrome-trace ("trace event") JSON of the most recent b2_step call made with collect_timing:
  * one complete event per layer and phase, pid = rank, tid = stream (0 main, 1 weight-gradient

@@ -71,6 +71,7 @@ SYMBOLS = {
     "b2_allreduce_sgd": (C.c_int, [_H, C.c_int]),
     "b2_allreduce_bench": (C.c_int, [_H, C.c_size_t, C.c_int, C.c_int, C.c_int, _dp, _dp]),
     "b2_get_timing": (C.c_int, [_H, _dp, _dp, C.POINTER(C.c_longlong)]),
+    "b2_get_gemm_busy_ms": (C.c_int, [_H, _dp]),
     "b2_reset_timing": (C.c_int, [_H]),
     "b2_write_trace": (C.c_int, [_H, C.c_char_p]),
     "b2_launch_counts": (C.c_int, [_H, C.POINTER(C.c_longlong), C.POINTER(C.c_longlong)]),

@@ -97,6 +97,7 @@ struct b2_handle {
     float start_ms, dur_ms;  // relative to the start of the b2_step call
   };
   std::vector<TraceEvent> trace;  // phases of the most recent timed b2_step call
+  double gemm_busy_ms = 0;        // time during which at least one GEMM of the step was running
   double step_ms = 0;
   long long steps = 0, launches = 0, tc_launches = 0;
   cudaGraphExec_t graph_exec = nullptr;
@@ -897,6 +898,20 @@ int b2_step(b2_handle* h, int iters) {
     for (auto ev : h->ev_phase) cudaEventDestroy(ev);
     h->ev_phase.clear();
     h->ev_iter = 0;
+    // forward / weight-gradient / input-gradient GEMMs overlap each other (two streams): the
+    // length of the union of their intervals is the time the GEMMs really occupied
+    std::vector<std::pair<float, float>> iv;
+    for (const auto& e : h->trace)
+      if (e.phase == B2_T_FWD || e.phase == B2_T_WGT_GRAD || e.phase == B2_T_BWD)
+        iv.push_back({e.start_ms, e.start_ms + e.dur_ms});
+    std::sort(iv.begin(), iv.end());
+    float cur_b = 0.f, cur_e = -1.f;
+    for (const auto& x : iv) {
+      if (cur_e < 0.f) { cur_b = x.first; cur_e = x.second; }
+      else if (x.first <= cur_e) { if (x.second > cur_e) cur_e = x.second; }
+      else { h->gemm_busy_ms += cur_e - cur_b; cur_b = x.first; cur_e = x.second; }
+    }
+    if (cur_e >= 0.f) h->gemm_busy_ms += cur_e - cur_b;
   }
   return check_status(h);
 }
@@ -1095,8 +1110,15 @@ int b2_write_trace(b2_handle* h, const char* path) {
   return B2_OK;
 }
 
+int b2_get_gemm_busy_ms(b2_handle* h, double* ms) {
+  if (!h || !ms) return B2_ERR_INVALID;
+  *ms = h->gemm_busy_ms;
+  return B2_OK;
+}
+
 int b2_reset_timing(b2_handle* h) {
   if (!h) return B2_ERR_INVALID;
+  h->gemm_busy_ms = 0;
   std::fill(h->phase_ms.begin(), h->phase_ms.end(), 0.0);
   h->step_ms = 0;
   h->steps = 0;

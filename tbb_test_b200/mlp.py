@@ -193,6 +193,11 @@ class MLP:
         self._ck(self.lib.b2_get_timing(self._h, ph, C.byref(ms), C.byref(n)))
         return np.array(ph[:]).reshape(self.L, K.T_NUM), ms.value, n.value
 
+    def gemm_busy_ms(self):
+        v = C.c_double()
+        self._ck(self.lib.b2_get_gemm_busy_ms(self._h, C.byref(v)))
+        return v.value
+
     def write_trace(self, path):
         self._ck(self.lib.b2_write_trace(self._h, str(path).encode()))
 
