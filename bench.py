@@ -407,9 +407,16 @@ def main():
     n_params = sum(nf[l] * nf[l + 1] for l in range(L))
     sgd_bytes = n_params * (14 if args.precision == "bf16" else 12)
     sgd_gbs = sgd_bytes / (per_phase["sgd_ms"] / 1e3) / 1e9 if per_phase["sgd_ms"] > 0 else 0.0
+    # DRAM bytes per GEMM launch (read + write) from an ncu capture of this kernel at
+    # 8192 x 4096 x 4096 bf16 (mean of a forward with ReLU, and a weight-gradient launch:
+    # profiles/gemm_tc_kernel_8192x4096x4096_bf16_ncu_full.md); other shapes were not captured
+    traffic = None
+    if args.precision == "bf16" and bl == 8192 and all(f == 4096 for f in nf):
+        traffic = (192.8e6 + 41.8e6 + 213.7e6 + 87.2e6 + 237.6e6 + 42.4e6) / 3
     roofline = {"bound": "tensor", "kernel": "gemm_tc_kernel (fwd + wgrad + dgrad launches; flops / time with a GEMM running)",
                 "achieved": achieved_tf, "peak": peak_tf, "unit": "TFLOP/s",
-                "frac": achieved_tf / peak_tf if peak_tf else None, "traffic": None,
+                "frac": achieved_tf / peak_tf if peak_tf else None, "traffic": traffic,
+                "traffic_note": "DRAM bytes per GEMM launch, ncu capture (algorithmic operands + result: 1.6e8)",
                 "peak_source": f"{peak_kind}: cuBLAS bf16 sustained ({peaks.get('bf16_tflops')} burst)",
                 "per_step_ms": per_phase,
                 "sgd": {"bound": "hbm", "achieved": sgd_gbs, "peak": peaks.get("hbm_gbs"), "unit": "GB/s",

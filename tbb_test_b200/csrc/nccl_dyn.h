@@ -21,9 +21,28 @@ enum { ncclSuccess = 0, ncclInProgress = 7 };
 enum { ncclFloat32 = 7, ncclBfloat16 = 9 };
 enum { ncclSum = 0 };
 
+// ncclConfig_t as laid out since NCCL 2.27 (the library reads `size` and `version` and
+// treats fields beyond an older caller's size as unset). Unset: INT_MIN / nullptr.
+struct ncclConfigCompat {
+  size_t size;
+  unsigned int magic;
+  unsigned int version;
+  int blocking, cgaClusterSize, minCTAs, maxCTAs;
+  const char* netName;
+  int splitShare, trafficClass;
+  const char* commName;
+  int collnetEnable, CTAPolicy, shrinkShare, nvlsCTAs;
+};
+inline ncclConfigCompat nccl_config_unset() {
+  const int U = -2147483647 - 1;
+  ncclConfigCompat c = {sizeof(ncclConfigCompat), 0xcafebeefu, 22703u, U, U, U, U, nullptr, U, U, nullptr, U, U, U, U};
+  return c;
+}
+
 struct NcclApi {
   int (*GetUniqueId)(ncclUniqueId*) = nullptr;
   int (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+  int (*CommInitRankConfig)(ncclComm_t*, int, ncclUniqueId, int, ncclConfigCompat*) = nullptr;
   int (*CommDestroy)(ncclComm_t) = nullptr;
   int (*CommAbort)(ncclComm_t) = nullptr;
   int (*AllReduce)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
@@ -67,6 +86,7 @@ inline NcclApi& nccl_api() {
     auto sym = [&](const char* n) { return dlsym(h, n); };
     api.GetUniqueId = (decltype(api.GetUniqueId))sym("ncclGetUniqueId");
     api.CommInitRank = (decltype(api.CommInitRank))sym("ncclCommInitRank");
+    api.CommInitRankConfig = (decltype(api.CommInitRankConfig))sym("ncclCommInitRankConfig");
     api.CommDestroy = (decltype(api.CommDestroy))sym("ncclCommDestroy");
     api.CommAbort = (decltype(api.CommAbort))sym("ncclCommAbort");
     api.AllReduce = (decltype(api.AllReduce))sym("ncclAllReduce");
