@@ -278,6 +278,8 @@ def main():
     ap.add_argument("--bucket-mb", type=int, default=-1,
                     help="gradient allreduce granularity in MiB (0 = per layer, -1 = library default)")
     ap.add_argument("--grad-bf16", action="store_true", help="bf16 weight gradients (configuration 5 style)")
+    ap.add_argument("--trace", default=None,
+                    help="write rank 0's Chrome trace (per-kernel intervals of the timed steps) to this file")
     ap.add_argument("--graph", action="store_true",
                     help="replay each step as one CUDA graph (latency-bound workloads c1/c3); per-phase "
                          "events are not available then and the roofline line uses the whole step time")
@@ -381,6 +383,8 @@ def main():
     l0, tc0 = dev.launch_counts()
     barrier()
     dev.step(args.steps)
+    if args.trace and rank == 0 and not args.graph:
+        dev.write_trace(args.trace)
     barrier()
     clocks = sampler.stop() if sampler else None  # idle samples are dropped, see ClockSampler.stop
     phase_ms, step_ms, nsteps = dev.timing()
@@ -428,16 +432,20 @@ def main():
                                  "note": "gradient ncclAllReduce calls timed on the side stream while GEMMs run"}
         # How much of the allreduce hides behind compute: 1 - (t_step - t_step,no allreduce) / t_allreduce,alone
         # (the reference's NO_ALL_REDUCE build gives the middle term, mlp_omp.cc:21). The buckets are
-        # those of the library's default rule: consecutive layers up to a quarter of all gradient bytes.
+        # those of the library's default rule: consecutive layers up to a quarter of all gradient bytes,
+        # each later bucket 1.5 times the one before on 4 or more GPUs.
         es = 2 if args.grad_bf16 else 4
         sizes = [nf[l] * nf[l + 1] * es for l in range(L - 1, -1, -1)]
         target = max(sum(sizes) // 4, 4 << 20) if args.bucket_mb < 0 else args.bucket_mb << 20
+        growth = 1.5 if (args.bucket_mb < 0 and world >= 4) else 1.0  # the library's default rule
+        growth = max(float(os.environ.get("B2_BUCKET_GROWTH", growth)), 1.0)
         buckets, acc = [], 0
         for i, b in enumerate(sizes):
             acc += b
             if acc >= target or i == len(sizes) - 1:
                 buckets.append(acc)
                 acc = 0
+                target = int(target * growth)
         t_alone = 0.0
         for b in buckets:
             barrier()

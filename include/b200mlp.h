@@ -84,8 +84,11 @@ typedef struct {
   int ar_bucket_mb;         /* gradient allreduce granularity: 0 = one collective per layer, issued as
                                soon as that layer's weight gradient is done (what the reference does per
                                layer, mlp_omp.cc:692-705); N > 0 = consecutive layers are summed
-                               together once they add up to N MiB; -1 = default: about a quarter of all
-                               gradient bytes per collective (large messages use NVLink far better) */
+                               together once they add up to N MiB; -1 = default: the first collective
+                               takes about a quarter of all gradient bytes (large messages use NVLink
+                               far better) and, with 4 or more GPUs, each later one 1.5 times the
+                               bytes of the one before (the sums then limit the step, so the first
+                               should start early and the rest be few) */
   float lr;                 /* SGD step (the reference hard-codes 1e-10, mlp_omp.cc:609) */
   const void* nccl_unique_id; /* B2_NCCL_ID_BYTES bytes from b2_nccl_unique_id(), shared by all
                                  ranks; NULL when world_size == 1 */

@@ -52,6 +52,9 @@ struct b2_handle {
   // both are persistent kernels, so the CTAs of one start on the SMs the other's last,
   // partial wave leaves idle instead of waiting for the whole kernel to drain.
   cudaStream_t s_wg = nullptr;
+  cudaStream_t s_upd = nullptr;  // SGD updates: off the collective's stream so that the next bucket's sum starts at once
+  cudaEvent_t ev_join_upd = nullptr;
+  std::vector<cudaEvent_t> ev_ar;  // per layer that closes a bucket: its allreduce is done
   cudaEvent_t ev_dz_last = nullptr;
   bool wg_stream = false;
   std::vector<float*> w;
@@ -143,14 +146,14 @@ void batch_range(int batch, int world, int rank, int* b, int* e) {
   *e = hi;
 }
 
-int make_site(b2_handle* h, Site& s, bool want_tc) {
+int make_site(b2_handle* h, Site& s, bool want_tc, int sms = 0) {
   s.d.ws = h->tc_ws;
   s.d.ws_flags = h->tc_ws_flags;
   s.active = s.d.M > 0 && s.d.N > 0 && s.d.K > 0;
   s.plan = nullptr;
   if (!s.active || !want_tc) return B2_OK;
   char why[128];
-  s.plan = gemm_tc_plan_create(s.d, h->gemm_sms, why, sizeof why);
+  s.plan = gemm_tc_plan_create(s.d, sms > 0 ? sms : h->gemm_sms, why, sizeof why);
   return B2_OK;  // a refused plan silently means the CUDA-core kernel serves this site
 }
 
@@ -222,6 +225,19 @@ int build_sites(b2_handle* h) {
   h->fwd.assign(L, Site());
   h->wgrad.assign(L, Site());
   h->dgrad.assign(L, Site());
+  // B2_BWD_SPLIT=p (experimental): while the weight-gradient stream is in use, its grids take
+  // p percent of the GEMM SMs and the input-gradient grids the rest, so that the two
+  // concurrent persistent kernels together stay inside the SMs not set aside for the collective
+  int wg_sms = 0, dg_sms = 0;
+  if (const char* e = getenv("B2_BWD_SPLIT")) {
+    const int pct = atoi(e);
+    if (h->wg_stream && pct > 0 && pct < 100) {
+      wg_sms = h->gemm_sms * pct / 100;
+      if (wg_sms < 1) wg_sms = 1;
+      dg_sms = h->gemm_sms - wg_sms;
+      if (dg_sms < 1) dg_sms = 1;
+    }
+  }
   for (int l = 0; l < L; ++l) {
     const int fi = h->nf[l], fo = h->nf[l + 1];
     const void* wop = h->op_type == T_BF16 ? (const void*)h->w16[l] : (const void*)h->w[l];
@@ -249,7 +265,7 @@ int build_sites(b2_handle* h) {
     g.in_type = h->op_type;
     g.out_type = h->grad_type;
     h->wgrad[l].d = g;
-    make_site(h, h->wgrad[l], tc);
+    make_site(h, h->wgrad[l], tc, wg_sms);
     // input gradient: dA[l] = dZ[l] * W[l] (mlp_omp.cc:655-671), masked by ReLU'(A[l])
     GemmDesc b{};
     b.M = bl; b.N = fi; b.K = fo;
@@ -263,7 +279,7 @@ int build_sites(b2_handle* h) {
     b.in_type = h->op_type;
     b.out_type = h->op_type;
     h->dgrad[l].d = b;
-    make_site(h, h->dgrad[l], tc);
+    make_site(h, h->dgrad[l], tc, dg_sms);
     if (l == 0 && !h->cfg.input_grad) h->dgrad[l].active = false;
     if (l == 0) {  // layer 0 reads the network input: one more pair of sites for the second slot
       h->fwd0_alt.d = f;
@@ -271,7 +287,7 @@ int build_sites(b2_handle* h) {
       make_site(h, h->fwd0_alt, tc);
       h->wgrad0_alt.d = g;
       h->wgrad0_alt.d.B = h->act0_alt;
-      make_site(h, h->wgrad0_alt, tc);
+      make_site(h, h->wgrad0_alt, tc, wg_sms);
     }
   }
   return B2_OK;
@@ -319,6 +335,8 @@ int enqueue_step(b2_handle* h, bool timed, int slot = 0) {
   const bool overlap = h->cfg.overlap != 0;
   const bool wg = overlap && h->wg_stream;
   cudaStream_t sm = h->s_main, sc = overlap ? h->s_comm : h->s_main, sw = wg ? h->s_wg : h->s_main;
+  cudaStream_t su = overlap ? h->s_upd : h->s_main;
+  const bool has_ar = h->cfg.world_size > 1 && h->cfg.allreduce;
   int rc;
   CK(h, cudaMemsetAsync(loss_acc, 0, sizeof(double), sm));
   for (int l = 0; l < L; ++l) {
@@ -351,21 +369,30 @@ int enqueue_step(b2_handle* h, bool timed, int slot = 0) {
     const bool closes_bucket = (h->bucket_low[l] == l);
     if (overlap) {
       CK(h, cudaEventRecord(h->ev_wgrad[l], sw));
-      if (closes_bucket) CK(h, cudaStreamWaitEvent(sc, h->ev_wgrad[l], 0));  // in-order stream: all of the bucket
+      // in-order weight-gradient stream: the event covers every layer of the bucket
+      if (closes_bucket) CK(h, cudaStreamWaitEvent(has_ar ? sc : su, h->ev_wgrad[l], 0));
     }
-    if (closes_bucket && (rc = bucket_allreduce(h, l, h->bucket_high[l], sc, timed))) return rc;
+    if (closes_bucket && has_ar) {
+      if ((rc = bucket_allreduce(h, l, h->bucket_high[l], sc, timed))) return rc;
+      if (overlap) {
+        CK(h, cudaEventRecord(h->ev_ar[l], sc));
+        CK(h, cudaStreamWaitEvent(su, h->ev_ar[l], 0));
+      }
+    }
     if (timed) CK(h, cudaEventRecord(phase_ev(h, l, B2_T_BWD, 0), sm));
     if ((rc = run_site(h, h->dgrad[l], sm))) return rc;
     if (timed) CK(h, cudaEventRecord(phase_ev(h, l, B2_T_BWD, 1), sm));
     if (overlap) CK(h, cudaEventRecord(h->ev_dgrad[l], sm));
     if (closes_bucket) {
-      // SGD of every layer of the bucket: after the sum, and after dgrad(l) - the last reader of
-      // the bucket's old weights on the in-order main stream
-      if (overlap) CK(h, cudaStreamWaitEvent(sc, h->ev_dgrad[l], 0));
-      for (int k = h->bucket_high[l]; k >= l; --k) {
-        if ((rc = layer_sgd(h, k, sc, timed))) return rc;
+      // SGD of every layer of the bucket, on its own stream so that the next bucket's sum does
+      // not queue behind it: after this bucket's sum, and after dgrad(l), the last reader of the
+      // bucket's old weights on the in-order main stream. Lowest layer first: it is the first
+      // one the next forward pass needs.
+      if (overlap) CK(h, cudaStreamWaitEvent(su, h->ev_dgrad[l], 0));
+      for (int k = l; k <= h->bucket_high[l]; ++k) {
+        if ((rc = layer_sgd(h, k, su, timed))) return rc;
         if (overlap) {
-          CK(h, cudaEventRecord(h->ev_upd[k], sc));
+          CK(h, cudaEventRecord(h->ev_upd[k], su));
           h->upd_pending[k] = 1;
         }
       }
@@ -381,6 +408,8 @@ int join_streams(b2_handle* h) {
   if (h->cfg.overlap) {
     CK(h, cudaEventRecord(h->ev_join, h->s_comm));
     CK(h, cudaStreamWaitEvent(h->s_main, h->ev_join, 0));
+    CK(h, cudaEventRecord(h->ev_join_upd, h->s_upd));
+    CK(h, cudaStreamWaitEvent(h->s_main, h->ev_join_upd, 0));
     for (auto& p : h->upd_pending) p = 0;
   }
   return B2_OK;
@@ -391,6 +420,13 @@ void free_all(b2_handle* h) {
   cudaSetDevice(h->cfg.device);
   if (h->s_main) cudaStreamSynchronize(h->s_main);
   if (h->s_comm) cudaStreamSynchronize(h->s_comm);
+  if (h->s_upd) {
+    cudaStreamSynchronize(h->s_upd);
+    cudaStreamDestroy(h->s_upd);
+  }
+  if (h->ev_join_upd) cudaEventDestroy(h->ev_join_upd);
+  for (auto e : h->ev_ar)
+    if (e) cudaEventDestroy(e);
   if (h->s_copy) cudaStreamSynchronize(h->s_copy);
   if (h->s_wg) {
     cudaStreamSynchronize(h->s_wg);
@@ -559,6 +595,7 @@ int b2_create(const b2_config* cfg, b2_handle** out) {
     int lo = 0, hi = 0;
     TRYCK(cudaDeviceGetStreamPriorityRange(&lo, &hi));
     TRYCK(cudaStreamCreateWithPriority(&h->s_comm, cudaStreamNonBlocking, hi));
+    TRYCK(cudaStreamCreateWithPriority(&h->s_upd, cudaStreamNonBlocking, hi));
   }
 
   TRYCK(cudaStreamCreateWithFlags(&h->s_wg, cudaStreamNonBlocking));
@@ -601,7 +638,8 @@ int b2_create(const b2_config* cfg, b2_handle** out) {
     }
     TRY(dev_alloc(h, &h->dw_slab, total * es));
     for (int l = 0; l < L; ++l) h->dw[l] = static_cast<char*>(h->dw_slab) + h->dw_off[l] * es;
-    // buckets: consecutive layers until about a quarter of all gradient bytes (at least 4 MiB);
+    // buckets: consecutive layers until about a quarter of all gradient bytes (at least 4 MiB),
+    // growing from bucket to bucket on 4 or more GPUs;
     // one layer per bucket when there is nothing to sum or the caller asks for it
     const bool multi = cfg->world_size > 1 && cfg->allreduce;
     size_t target = total_bytes_all / 4;
@@ -612,6 +650,13 @@ int b2_create(const b2_config* cfg, b2_handle** out) {
     h->bucket_high.assign(L, 0);
     int high = L - 1;
     size_t acc = 0;
+    // Default rule only: with 4 or more GPUs the chain of collectives is longer than the
+    // backward pass, so later buckets grow (fewer collectives) while the first stays small
+    // (starts early). With 2 GPUs the step is compute-bound and a small last bucket keeps
+    // the tail after the last weight gradient short. B2_BUCKET_GROWTH overrides the factor.
+    double growth = (cfg->ar_bucket_mb < 0 && cfg->world_size >= 4) ? 1.5 : 1.0;
+    if (const char* e = getenv("B2_BUCKET_GROWTH")) growth = atof(e);
+    if (growth < 1.0) growth = 1.0;
     for (int l = L - 1; l >= 0; --l) {
       acc += (size_t)h->nf[l + 1] * h->nf[l] * es;
       if (acc >= target || l == 0) {
@@ -621,6 +666,7 @@ int b2_create(const b2_config* cfg, b2_handle** out) {
         }
         high = l - 1;
         acc = 0;
+        target = (size_t)((double)target * growth);
       }
     }
   }
@@ -652,15 +698,18 @@ int b2_create(const b2_config* cfg, b2_handle** out) {
   h->ev_wgrad.assign(L, nullptr);
   h->ev_dgrad.assign(L, nullptr);
   h->ev_upd.assign(L, nullptr);
+  h->ev_ar.assign(L, nullptr);
   h->upd_pending.assign(L, 0);
   for (int l = 0; l < L; ++l) {
     TRYCK(cudaEventCreateWithFlags(&h->ev_wgrad[l], cudaEventDisableTiming));
     TRYCK(cudaEventCreateWithFlags(&h->ev_dgrad[l], cudaEventDisableTiming));
     TRYCK(cudaEventCreateWithFlags(&h->ev_upd[l], cudaEventDisableTiming));
+    TRYCK(cudaEventCreateWithFlags(&h->ev_ar[l], cudaEventDisableTiming));
   }
   TRYCK(cudaEventCreate(&h->ev_t0));
   TRYCK(cudaEventCreate(&h->ev_t1));
   TRYCK(cudaEventCreateWithFlags(&h->ev_join, cudaEventDisableTiming));
+  TRYCK(cudaEventCreateWithFlags(&h->ev_join_upd, cudaEventDisableTiming));
   TRYCK(cudaEventCreateWithFlags(&h->ev_fork, cudaEventDisableTiming));
   h->phase_ms.assign((size_t)L * B2_T_NUM, 0.0);
 
@@ -807,6 +856,7 @@ int b2_sync(b2_handle* h) {
   ENTER(h);
   CK(h, cudaStreamSynchronize(h->s_main));
   CK(h, cudaStreamSynchronize(h->s_comm));
+  CK(h, cudaStreamSynchronize(h->s_upd));
   CK(h, cudaStreamSynchronize(h->s_wg));
   return check_status(h);
 }
@@ -863,6 +913,7 @@ int b2_step(b2_handle* h, int iters) {
   if (graph && !h->graph_exec) {
     CK(h, cudaStreamSynchronize(h->s_main));
     CK(h, cudaStreamSynchronize(h->s_comm));
+    CK(h, cudaStreamSynchronize(h->s_upd));
     if ((rc = capture_graph(h))) return rc;
   }
   if (timed) {  // one event pair per (step, layer, phase): nothing is read back before the end
@@ -885,6 +936,7 @@ int b2_step(b2_handle* h, int iters) {
   CK(h, cudaEventRecord(h->ev_t1, h->s_main));
   CK(h, cudaStreamSynchronize(h->s_main));
   CK(h, cudaStreamSynchronize(h->s_comm));
+  CK(h, cudaStreamSynchronize(h->s_upd));
   float ms = 0.f;
   CK(h, cudaEventElapsedTime(&ms, h->ev_t0, h->ev_t1));
   h->step_ms += ms;
@@ -1105,8 +1157,8 @@ int b2_write_trace(b2_handle* h, const char* path) {
   FILE* f = fopen(path, "w");
   if (!f) return fail(h, B2_ERR_INVALID, "cannot open %s", path);
   static const char* names[B2_T_NUM] = {"fwd", "wgt_grad", "bwd", "wgt_update", "allreduce"};
-  // one "thread" per stream: main (fwd, bwd), weight-gradient stream, side stream (allreduce, update)
-  static const int tid[B2_T_NUM] = {0, 1, 0, 2, 2};
+  // one "thread" per stream: main (fwd, bwd), weight-gradient stream, collective stream, update stream
+  static const int tid[B2_T_NUM] = {0, 1, 0, 3, 2};
   fprintf(f, "[\n");
   for (size_t i = 0; i < h->trace.size(); ++i) {
     const auto& e = h->trace[i];
