@@ -284,6 +284,8 @@ def main():
                     help="replay each step as one CUDA graph (latency-bound workloads c1/c3); per-phase "
                          "events are not available then and the roofline line uses the whole step time")
     args = ap.parse_args()
+    if args.graph and args.gpus > 1:
+        ap.error("--graph is for single-GPU runs: the library refuses graph replay together with the allreduce")
 
     rank, world = env_int("RANK", 0), env_int("WORLD_SIZE", 1)
     local_rank = env_int("LOCAL_RANK", 0)

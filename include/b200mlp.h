@@ -75,7 +75,8 @@ typedef struct {
                                remaining backward GEMMs (OVERLAP_ALL_REDUCE, mlp_omp.cc:23) */
   int input_grad;           /* 1 = also compute dA[0] like the reference (mlp_omp.cc:656) */
   int collect_timing;       /* 1 = per-phase CUDA-event timing (sum_times, mlp_bench_common.h:35) */
-  int use_graph;            /* 1 = replay each step as one CUDA graph */
+  int use_graph;            /* 1 = replay each step as one CUDA graph (refused with B2_ERR_UNSUPPORTED
+                               when world_size > 1 and allreduce = 1) */
   int force_simt;           /* 1 = never use the tensor-core kernels (debugging aid) */
   int comm_sms;             /* SMs the persistent GEMM kernels leave free for the collective's CTAs
                                while allreduce and GEMMs overlap (the counterpart of the threads the

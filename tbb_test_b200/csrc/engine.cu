@@ -537,6 +537,10 @@ int b2_create(const b2_config* cfg, b2_handle** out) {
     if (cfg->nfeatures[i] < 1) return fail(nullptr, B2_ERR_INVALID, "nfeatures[%d] must be positive", i);
   if (cfg->world_size > 1 && cfg->allreduce && !cfg->nccl_unique_id)
     return fail(nullptr, B2_ERR_INVALID, "world_size > 1 needs nccl_unique_id");
+  // A captured step that contains collectives did not complete on two GPUs (cause not found);
+  // graph replay is for the latency-bound single-GPU configurations.
+  if (cfg->use_graph && cfg->world_size > 1 && cfg->allreduce)
+    return fail(nullptr, B2_ERR_UNSUPPORTED, "use_graph is not supported together with the gradient allreduce");
 
   int ndev = 0;
   cudaError_t e = cudaGetDeviceCount(&ndev);
