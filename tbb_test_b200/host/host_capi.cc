@@ -3,6 +3,7 @@
 // ctypes, with golden vectors produced by the reference's own functions.
 #include <cstring>
 
+#include "HyperCubeAllReduce.h"
 #include "TwistedHyperCube.h"
 #include "mlp_bench_common.h"
 
@@ -41,6 +42,26 @@ void b2h_hypercube(int twisted, int num_nodes, int shift, int id, int dim, int* 
     out3[1] = c.RecvLocation(id, dim);
     out3[2] = c.SendLocation(id, dim);
   }
+}
+
+// Allreduce of `num_nodes` buffers of `count` floats through the hypercube addressing.
+// Returns 1 on success, 0 when the addressing is not a consistent schedule.
+int b2h_hypercube_allreduce(int twisted, int num_nodes, int shift, float* const* bufs, size_t count, int threaded) {
+  if (twisted) return hypercube_allreduce(TwistedHyperCube(num_nodes, shift), bufs, count, threaded != 0) ? 1 : 0;
+  return hypercube_allreduce(HyperCube(num_nodes, shift), bufs, count, threaded != 0) ? 1 : 0;
+}
+
+// The 2 * log2(num_nodes) steps of node `id`, 5 ints each: dim, peer, first_chunk, num_chunks, reduce.
+int b2h_hypercube_steps(int twisted, int num_nodes, int shift, int id, int* out, int max_steps) {
+  std::vector<HyperCubeStep> st = twisted ? hypercube_allreduce_steps(TwistedHyperCube(num_nodes, shift), id)
+                                          : hypercube_allreduce_steps(HyperCube(num_nodes, shift), id);
+  int n = 0;
+  for (const auto& s : st) {
+    if (n >= max_steps) break;
+    int* o = out + 5 * n++;
+    o[0] = s.dim; o[1] = s.peer; o[2] = s.first_chunk; o[3] = s.num_chunks; o[4] = s.reduce ? 1 : 0;
+  }
+  return (int)st.size();
 }
 
 void b2h_ring_info(int nsock, int sid, int task, int* out3) {

@@ -75,6 +75,79 @@ def test_hypercube_is_a_valid_halving_schedule(host):
                 assert sorted(owned) == list(range(n))
 
 
+def _cube_allreduce(host, twisted, n, shift, bufs, threaded):
+    fp = C.POINTER(C.c_float)
+    arr = (fp * n)(*[b.ctypes.data_as(fp) for b in bufs])
+    host.b2h_hypercube_allreduce.restype = C.c_int
+    host.b2h_hypercube_allreduce.argtypes = [C.c_int, C.c_int, C.c_int, C.POINTER(fp), C.c_size_t, C.c_int]
+    return host.b2h_hypercube_allreduce(twisted, n, shift, arr, bufs[0].size, int(threaded))
+
+
+@pytest.mark.parametrize("threaded", [False, True])
+def test_hypercube_allreduce_data_path(host, threaded):
+    """Recursive halving + doubling driven by Peer / RecvLocation / SendLocation sums the
+    buffers of all nodes into every node: exact on small integers (any summation order),
+    for lengths that do and do not divide by the node count, the empty buffer included."""
+    rng = np.random.default_rng(5)
+    for twisted in (0, 1):
+        for n, dims in ((2, 1), (4, 2), (8, 3)):
+            for shift in range(dims):
+                if twisted and n == 8 and shift == 2:
+                    continue
+                for count in (0, 1, n - 1, n, 1000, 4099):
+                    bufs = [rng.integers(-50, 50, count).astype(np.float32) for _ in range(n)]
+                    want = np.sum(bufs, axis=0, dtype=np.float64).astype(np.float32)
+                    assert _cube_allreduce(host, twisted, n, shift, bufs, threaded) == 1
+                    for b in bufs:
+                        assert np.array_equal(b, want), (twisted, n, shift, count)
+
+
+def test_hypercube_allreduce_is_deterministic_and_close_on_reals(host):
+    """On real data every node ends with bit-identical values (each chunk is summed once,
+    by its owner, and copied), within float rounding of the exact sum."""
+    rng = np.random.default_rng(6)
+    n, count = 8, 6000
+    src = [rng.uniform(-1, 1, count).astype(np.float32) for _ in range(n)]
+    runs = []
+    for threaded in (False, True):
+        bufs = [b.copy() for b in src]
+        assert _cube_allreduce(host, 1, n, 1, bufs, threaded) == 1
+        assert all(np.array_equal(bufs[0], b) for b in bufs[1:])
+        runs.append(bufs[0])
+    assert np.array_equal(runs[0], runs[1])
+    assert np.abs(runs[0] - np.sum(src, axis=0, dtype=np.float64)).max() <= 1e-5  # mlp_omp.cc:360 bound
+
+
+def test_hypercube_allreduce_refuses_the_inconsistent_schedule(host):
+    """Shift 2 of the 8-node twisted cube sends and receives the same location in
+    dimensions 1 and 2; the data path refuses it and leaves the buffers alone."""
+    bufs = [np.full(64, i, np.float32) for i in range(8)]
+    assert _cube_allreduce(host, 1, 8, 2, bufs, False) == 0
+    assert all(np.array_equal(b, np.full(64, i, np.float32)) for i, b in enumerate(bufs))
+
+
+def test_hypercube_steps_follow_the_golden_tables(host, gold):
+    """The step list a device implementation would execute: halving from the highest
+    dimension down (reading the range the node keeps), doubling upwards (reading the
+    range the peer finished), peers and locations as in the reference's tables."""
+    table = {(t, n, s, i, d): exp for t, n, s, i, d, *exp in gold["hypercube"]}
+    host.b2h_hypercube_steps.restype = C.c_int
+    for (t, n, s) in sorted({k[:3] for k in table}):
+        if t and n == 8 and s == 2:
+            continue
+        dims = n.bit_length() - 1
+        for i in range(n):
+            out = (C.c_int * (5 * 2 * dims))()
+            assert host.b2h_hypercube_steps(t, n, s, i, out, 2 * dims) == 2 * dims
+            steps = [tuple(out[5 * k:5 * k + 5]) for k in range(2 * dims)]
+            for k, d in enumerate(range(dims - 1, -1, -1)):
+                peer, recv, _send = table[(t, n, s, i, d)]
+                assert steps[k] == (d, peer, recv, 1 << d, 1)
+            for k, d in enumerate(range(dims)):
+                peer = table[(t, n, s, i, d)][0]
+                assert steps[dims + k] == (d, peer, table[(t, n, s, peer, d)][1], 1 << d, 0)
+
+
 def test_ring_info(host, gold):
     for nsock, sid, task, *exp in gold["ring_info"]:
         assert _call(host.b2h_ring_info, 3, nsock, sid, task) == exp
