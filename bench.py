@@ -40,7 +40,18 @@ WORKLOADS = {
     "c1": ([1024] * 6, 1024, ("uniform", 1.0 / 32), "5 x 1024^2, batch 1024"),
     "c3": ([512] * 21, 2048, ("uniform", 512 ** -0.5), "20 x 512^2, batch 2048"),
     "c4": ([4096] * 9, 8192, ("uniform", 1.0 / 64), "8 x 4096^2, batch 8192"),
+    # bf16 operands and bf16 weight gradients, fp32 master weights (implies --grad-bf16)
+    "c5": ([8192] * 17, 16384, ("normal", 8192 ** -0.5), "16 x 8192^2, batch 16384, bf16 gradients"),
 }
+
+
+def draw_weights(rng, winit, shape):
+    """Seeded weights of one layer: U(-a, a) or N(0, a^2)."""
+    import numpy as np
+    kind, a = winit
+    if kind == "normal":
+        return (rng.standard_normal(shape, dtype=np.float32) * np.float32(a)).astype(np.float32)
+    return rng.uniform(-a, a, shape).astype(np.float32)
 
 
 def env_int(name, default):
@@ -292,6 +303,10 @@ def main():
     if args.workload == "c2":
         return allreduce_sweep(args, rank, world, local_rank)
     nf, batch, winit, desc = WORKLOADS[args.workload]
+    if args.workload == "c5":
+        if args.precision != "bf16":
+            ap.error("workload c5 is defined for bf16 operands")
+        args.grad_bf16 = True
     warmup = max(args.warmup, 3)
     L = len(nf) - 1
     cfg_common = {"workload": f"{args.workload}: MLP {desc}, ReLU, +-1 targets, SGD lr 0.01; "
@@ -367,8 +382,7 @@ def main():
     # draws the same weights and only its own rows of the batch
     rng_w = np.random.default_rng(0)
     for l in range(L):
-        a = winit[1]
-        dev.upload_weights(l, rng_w.uniform(-a, a, (nf[l + 1], nf[l])).astype(np.float32))
+        dev.upload_weights(l, draw_weights(rng_w, winit, (nf[l + 1], nf[l])))
     x_host = pinned_array((batch, nf[0]))
     t_host = pinned_array((batch, nf[-1]))
     rng_x = np.random.default_rng([1, rank])
@@ -457,7 +471,7 @@ def main():
                    lr=0.01, allreduce=False, grad_bf16=args.grad_bf16)
         rng_n = np.random.default_rng(0)
         for l in range(L):
-            noar.upload_weights(l, rng_n.uniform(-winit[1], winit[1], (nf[l + 1], nf[l])).astype(np.float32))
+            noar.upload_weights(l, draw_weights(rng_n, winit, (nf[l + 1], nf[l])))
         noar.upload_input(x_host)
         noar.upload_target(t_host)
         noar.step(warmup)
@@ -485,7 +499,7 @@ def main():
                   comm_sms=args.comm_sms, grad_bf16=args.grad_bf16, ar_bucket_mb=args.bucket_mb)
         rng_w = np.random.default_rng(0)
         for l in range(L):
-            dev.upload_weights(l, rng_w.uniform(-winit[1], winit[1], (nf[l + 1], nf[l])).astype(np.float32))
+            dev.upload_weights(l, draw_weights(rng_w, winit, (nf[l + 1], nf[l])))
         xp = x_host.ctypes.data_as(K._fp)
         tp = t_host.ctypes.data_as(K._fp)
 
