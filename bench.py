@@ -220,9 +220,26 @@ def allreduce_sweep(args, rank, world, local_rank):
         except Exception as e:  # no prebuilt reference on this machine
             table, kind = [{"error": str(e)}], "unavailable"
         best = max((r.get("busbw_gbs", 0.0) for r in table), default=0.0)
+        # the TwistedHyperCube addressing as a data path (recursive halving + doubling between host
+        # threads; the reference declares the interface only): this repository's host code
+        cube = []
+        try:
+            import ctypes as C
+            from tbb_test_b200 import build as B
+            H = C.CDLL(B.HOST_LIB)
+            H.b2h_time_hypercube_allreduce.restype = C.c_double
+            H.b2h_time_hypercube_allreduce.argtypes = [C.c_int, C.c_int, C.c_int, C.c_size_t, C.c_int]
+            for nbytes in (1 << 12, 1 << 16, 1 << 20, 1 << 24, 1 << 26):
+                t = H.b2h_time_hypercube_allreduce(1 if socks == 8 else 0, socks, 0, nbytes // 4,
+                                                   50 if nbytes <= (1 << 20) else 3)
+                cube.append({"bytes": nbytes, "ms": t * 1e3,
+                             "busbw_gbs": nbytes * 2 * (socks - 1) / socks / t / 1e9 if t > 0 else None})
+        except (OSError, AttributeError) as e:
+            cube = [{"error": str(e)}]
         cpu = {"value": best, "unit": "GB/s", "cores": socks, "kind": kind,
                "sample": f"reference update_weight (ring reduce-scatter + SGD + allgather), {socks} sockets x 1 "
-                         "thread on the host cores, sizes 4 KB .. 64 MB", "table": table}
+                         "thread on the host cores, sizes 4 KB .. 64 MB", "table": table,
+               "twisted_hypercube_host_path": cube}
         line = {"impl": "reference", "metric": "allreduce_busbw", "value": best, "unit": "GB/s", "n_gpus": 0,
                 "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": None, "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",

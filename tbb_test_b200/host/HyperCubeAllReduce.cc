@@ -1,9 +1,8 @@
 #include "HyperCubeAllReduce.h"
 
 #include <algorithm>
-#include <condition_variable>
+#include <atomic>
 #include <cstring>
-#include <mutex>
 #include <thread>
 
 std::vector<HyperCubeStep> hypercube_allreduce_steps(const HyperCube& cube, int id) {
@@ -67,32 +66,32 @@ void run_step(const HyperCubeStep& s, float* mine, const float* theirs, size_t c
   }
 }
 
-// Reusable barrier for the per-node threads.
+// Reusable barrier for the per-node threads: counts arrivals, the last one opens the next
+// generation; waiters spin briefly, then yield (the nodes may outnumber the cores).
 class StepBarrier {
  public:
   explicit StepBarrier(int n) : n_(n) {}
   void wait() {
-    std::unique_lock<std::mutex> lk(m_);
-    const long long gen = gen_;
-    if (++arrived_ == n_) {
-      arrived_ = 0;
-      ++gen_;
-      cv_.notify_all();
-    } else {
-      cv_.wait(lk, [&] { return gen_ != gen; });
+    const unsigned gen = gen_.load(std::memory_order_acquire);
+    if (arrived_.fetch_add(1, std::memory_order_acq_rel) + 1 == n_) {
+      arrived_.store(0, std::memory_order_relaxed);
+      gen_.store(gen + 1, std::memory_order_release);
+      return;
     }
+    for (int spins = 0; gen_.load(std::memory_order_acquire) == gen; ++spins)
+      if (spins > 2000) std::this_thread::yield();
   }
 
  private:
-  std::mutex m_;
-  std::condition_variable cv_;
-  int n_, arrived_ = 0;
-  long long gen_ = 0;
+  const int n_;
+  std::atomic<int> arrived_{0};
+  std::atomic<unsigned> gen_{0};
 };
 
 }  // namespace
 
-bool hypercube_allreduce(const HyperCube& cube, float* const* bufs, size_t count, bool threaded) {
+bool hypercube_allreduce(const HyperCube& cube, float* const* bufs, size_t count, bool threaded,
+                         int iterations) {
   if (!hypercube_schedule_is_consistent(cube)) return false;
   const int N = cube.NumNodes();
   std::vector<std::vector<HyperCubeStep>> steps(N);
@@ -102,18 +101,20 @@ bool hypercube_allreduce(const HyperCube& cube, float* const* bufs, size_t count
   // halves of a range while halving, disjoint finished ranges while doubling), so a barrier
   // between steps is all the ordering needed.
   if (!threaded) {
-    for (size_t s = 0; s < nsteps; ++s)
-      for (int i = 0; i < N; ++i) run_step(steps[i][s], bufs[i], bufs[steps[i][s].peer], count, N);
+    for (int it = 0; it < iterations; ++it)
+      for (size_t s = 0; s < nsteps; ++s)
+        for (int i = 0; i < N; ++i) run_step(steps[i][s], bufs[i], bufs[steps[i][s].peer], count, N);
     return true;
   }
   StepBarrier barrier(N);
   std::vector<std::thread> pool;
   for (int i = 0; i < N; ++i)
     pool.emplace_back([&, i] {
-      for (size_t s = 0; s < nsteps; ++s) {
-        run_step(steps[i][s], bufs[i], bufs[steps[i][s].peer], count, N);
-        barrier.wait();
-      }
+      for (int it = 0; it < iterations; ++it)
+        for (size_t s = 0; s < nsteps; ++s) {
+          run_step(steps[i][s], bufs[i], bufs[steps[i][s].peer], count, N);
+          barrier.wait();
+        }
     });
   for (auto& t : pool) t.join();
   return true;

@@ -40,5 +40,7 @@ bool hypercube_schedule_is_consistent(const HyperCube& cube);
 
 // In-place sum of bufs[0..N) (each `count` floats) into every buffer. One thread per node
 // when `threaded`, otherwise the nodes are walked step by step on the calling thread.
-// Returns false (buffers untouched) when the schedule is inconsistent.
-bool hypercube_allreduce(const HyperCube& cube, float* const* bufs, size_t count, bool threaded);
+// `iterations` > 1 repeats the allreduce on its own result (for timing: the node threads are
+// started once). Returns false (buffers untouched) when the schedule is inconsistent.
+bool hypercube_allreduce(const HyperCube& cube, float* const* bufs, size_t count, bool threaded,
+                         int iterations = 1);

@@ -1,9 +1,12 @@
 // C exports of the host-side mirror (Partition, TwistedHyperCube, ring tables,
 // Matrix layout, seeded fills) so that the test-suite can compare them, through
 // ctypes, with golden vectors produced by the reference's own functions.
+#include <chrono>
 #include <cstring>
+#include <vector>
 
 #include "HyperCubeAllReduce.h"
+#include "b2_rng.h"
 #include "TwistedHyperCube.h"
 #include "mlp_bench_common.h"
 
@@ -49,6 +52,27 @@ void b2h_hypercube(int twisted, int num_nodes, int shift, int id, int dim, int* 
 int b2h_hypercube_allreduce(int twisted, int num_nodes, int shift, float* const* bufs, size_t count, int threaded) {
   if (twisted) return hypercube_allreduce(TwistedHyperCube(num_nodes, shift), bufs, count, threaded != 0) ? 1 : 0;
   return hypercube_allreduce(HyperCube(num_nodes, shift), bufs, count, threaded != 0) ? 1 : 0;
+}
+
+// Seconds per allreduce of `count` floats over `num_nodes` host threads (one per node), buffers
+// U(-1,1) from seed = node id; 0 when the addressing is inconsistent.
+double b2h_time_hypercube_allreduce(int twisted, int num_nodes, int shift, size_t count, int iterations) {
+  std::vector<std::vector<float>> store(num_nodes, std::vector<float>(count));
+  std::vector<float*> bufs(num_nodes);
+  for (int i = 0; i < num_nodes; ++i) {
+    for (size_t k = 0; k < count; ++k) store[i][k] = b2_rng_uniform((uint64_t)i, k, -1.f, 1.f);
+    bufs[i] = store[i].data();
+  }
+  HyperCube plain(num_nodes, shift);
+  TwistedHyperCube twist(twisted ? num_nodes : 2, twisted ? shift : 0);
+  const HyperCube& cube = twisted ? static_cast<const HyperCube&>(twist) : plain;
+  if (!hypercube_allreduce(cube, bufs.data(), count, true, 1)) return 0.0;  // warm-up
+  // keep the values bounded over the timed repetitions
+  for (int i = 0; i < num_nodes; ++i)
+    for (size_t k = 0; k < count; ++k) store[i][k] *= 1e-6f;
+  const auto t0 = std::chrono::steady_clock::now();
+  hypercube_allreduce(cube, bufs.data(), count, true, iterations);
+  return std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count() / iterations;
 }
 
 // The 2 * log2(num_nodes) steps of node `id`, 5 ints each: dim, peer, first_chunk, num_chunks, reduce.
