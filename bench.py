@@ -45,6 +45,23 @@ WORKLOADS = {
 }
 
 
+def gradient_buckets(layer_bytes, world, bucket_mb):
+    """Bytes of each gradient collective of one step, in issue order, from the library's own
+    rule (csrc/bucket_plan.h through the host library)."""
+    import ctypes as C
+    from tbb_test_b200 import build as B
+    H = C.CDLL(B.HOST_LIB)
+    n = len(layer_bytes)
+    low, high = (C.c_int * n)(), (C.c_int * n)()
+    growth = float(os.environ.get("B2_BUCKET_GROWTH", 0.0))
+    H.b2h_plan_buckets((C.c_size_t * n)(*layer_bytes), n, world, 1, bucket_mb, C.c_double(growth), low, high)
+    out, l = [], n - 1
+    while l >= 0:
+        out.append(sum(layer_bytes[low[l]:high[l] + 1]))
+        l = low[l] - 1
+    return out
+
+
 def draw_weights(rng, winit, shape):
     """Seeded weights of one layer: U(-a, a) or N(0, a^2)."""
     import numpy as np
@@ -468,17 +485,7 @@ def main():
         # those of the library's default rule: consecutive layers up to a quarter of all gradient bytes,
         # each later bucket 1.5 times the one before on 4 or more GPUs.
         es = 2 if args.grad_bf16 else 4
-        sizes = [nf[l] * nf[l + 1] * es for l in range(L - 1, -1, -1)]
-        target = max(sum(sizes) // 4, 4 << 20) if args.bucket_mb < 0 else args.bucket_mb << 20
-        growth = 1.5 if (args.bucket_mb < 0 and world >= 4) else 1.0  # the library's default rule
-        growth = max(float(os.environ.get("B2_BUCKET_GROWTH", growth)), 1.0)
-        buckets, acc = [], 0
-        for i, b in enumerate(sizes):
-            acc += b
-            if acc >= target or i == len(sizes) - 1:
-                buckets.append(acc)
-                acc = 0
-                target = int(target * growth)
+        buckets = gradient_buckets([nf[l] * nf[l + 1] * es for l in range(L)], world, args.bucket_mb)
         t_alone = 0.0
         for b in buckets:
             barrier()

@@ -23,6 +23,7 @@
 #include <vector>
 
 #include "../../include/b200mlp.h"
+#include "bucket_plan.h"
 #include "common.cuh"
 #include "nccl_dyn.h"
 
@@ -633,46 +634,24 @@ int b2_create(const b2_config* cfg, b2_handle** out) {
     // gradient slab, last layer first; every layer starts on a 256-byte boundary
     h->dw_off.assign(L, 0);
     const size_t es = esize(h->grad_type), align_elems = 256 / es;
-    size_t total = 0, total_bytes_all = 0;
+    size_t total = 0;
     for (int l = L - 1; l >= 0; --l) {
       h->dw_off[l] = total;
       const size_t nw = (size_t)h->nf[l + 1] * h->nf[l];
       total += (nw + align_elems - 1) / align_elems * align_elems;
-      total_bytes_all += nw * es;
     }
     TRY(dev_alloc(h, &h->dw_slab, total * es));
     for (int l = 0; l < L; ++l) h->dw[l] = static_cast<char*>(h->dw_slab) + h->dw_off[l] * es;
-    // buckets: consecutive layers until about a quarter of all gradient bytes (at least 4 MiB),
-    // growing from bucket to bucket on 4 or more GPUs;
-    // one layer per bucket when there is nothing to sum or the caller asks for it
-    const bool multi = cfg->world_size > 1 && cfg->allreduce;
-    size_t target = total_bytes_all / 4;
-    if (target < ((size_t)4 << 20)) target = (size_t)4 << 20;
-    if (cfg->ar_bucket_mb == 0 || !multi) target = 0;
-    if (cfg->ar_bucket_mb > 0) target = (size_t)cfg->ar_bucket_mb << 20;
+    // buckets of consecutive layers (rule and rationale: bucket_plan.h); B2_BUCKET_GROWTH
+    // overrides the factor between consecutive buckets
+    std::vector<size_t> layer_bytes(L);
+    for (int l = 0; l < L; ++l) layer_bytes[l] = (size_t)h->nf[l + 1] * h->nf[l] * es;
+    double growth = 0.0;
+    if (const char* e = getenv("B2_BUCKET_GROWTH")) growth = atof(e);
     h->bucket_low.assign(L, 0);
     h->bucket_high.assign(L, 0);
-    int high = L - 1;
-    size_t acc = 0;
-    // Default rule only: with 4 or more GPUs the chain of collectives is longer than the
-    // backward pass, so later buckets grow (fewer collectives) while the first stays small
-    // (starts early). With 2 GPUs the step is compute-bound and a small last bucket keeps
-    // the tail after the last weight gradient short. B2_BUCKET_GROWTH overrides the factor.
-    double growth = (cfg->ar_bucket_mb < 0 && cfg->world_size >= 4) ? 1.5 : 1.0;
-    if (const char* e = getenv("B2_BUCKET_GROWTH")) growth = atof(e);
-    if (growth < 1.0) growth = 1.0;
-    for (int l = L - 1; l >= 0; --l) {
-      acc += (size_t)h->nf[l + 1] * h->nf[l] * es;
-      if (acc >= target || l == 0) {
-        for (int k = high; k >= l; --k) {
-          h->bucket_low[k] = l;
-          h->bucket_high[k] = high;
-        }
-        high = l - 1;
-        acc = 0;
-        target = (size_t)((double)target * growth);
-      }
-    }
+    plan_gradient_buckets(layer_bytes.data(), L, cfg->world_size, cfg->allreduce != 0, cfg->ar_bucket_mb, growth,
+                          h->bucket_low.data(), h->bucket_high.data());
   }
   TRY(dev_alloc(h, &h->y, bl * h->nf[L] * 4));
   TRY(dev_alloc(h, &h->target, bl * h->nf[L] * 4));

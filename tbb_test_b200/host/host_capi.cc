@@ -5,6 +5,7 @@
 #include <cstring>
 #include <vector>
 
+#include "../csrc/bucket_plan.h"
 #include "HyperCubeAllReduce.h"
 #include "b2_rng.h"
 #include "TwistedHyperCube.h"
@@ -86,6 +87,13 @@ int b2h_hypercube_steps(int twisted, int num_nodes, int shift, int id, int* out,
     o[0] = s.dim; o[1] = s.peer; o[2] = s.first_chunk; o[3] = s.num_chunks; o[4] = s.reduce ? 1 : 0;
   }
   return (int)st.size();
+}
+
+// The library's gradient-bucket rule (csrc/bucket_plan.h): lowest / highest layer of each layer's bucket.
+void b2h_plan_buckets(const size_t* layer_bytes, int nlayers, int world_size, int allreduce, int ar_bucket_mb,
+                      double growth, int* bucket_low, int* bucket_high) {
+  b2::plan_gradient_buckets(layer_bytes, nlayers, world_size, allreduce != 0, ar_bucket_mb, growth, bucket_low,
+                            bucket_high);
 }
 
 void b2h_ring_info(int nsock, int sid, int task, int* out3) {

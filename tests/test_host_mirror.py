@@ -177,3 +177,52 @@ def test_init_matrices_draws_the_pinned_stream(host, oracle):
         pos += nf[l + 1] * nf[l]
         assert np.array_equal(ws[l][:nf[l + 1]], exp)
         assert np.array_equal(ws[l][nf[l + 1]:], exp)
+
+
+def _plan(host, layer_bytes, world, bucket_mb, growth=0.0, allreduce=1):
+    n = len(layer_bytes)
+    low, high = (C.c_int * n)(), (C.c_int * n)()
+    host.b2h_plan_buckets.argtypes = [C.POINTER(C.c_size_t), C.c_int, C.c_int, C.c_int, C.c_int, C.c_double,
+                                      C.POINTER(C.c_int), C.POINTER(C.c_int)]
+    host.b2h_plan_buckets((C.c_size_t * n)(*layer_bytes), n, world, allreduce, bucket_mb, growth, low, high)
+    return list(low), list(high)
+
+
+def test_gradient_bucket_rule(host):
+    """The rule the library applies to group layers into one collective: equal quarter-size
+    buckets on 2 GPUs, growing ones on 4 or more, one layer per bucket on request or when there
+    is nothing to sum; every layer belongs to exactly one bucket of consecutive layers."""
+    mib = 1 << 20
+    c4 = [64 * mib] * 8
+    assert _plan(host, c4, 2, -1) == ([0, 0, 2, 2, 4, 4, 6, 6], [1, 1, 3, 3, 5, 5, 7, 7])
+    assert _plan(host, c4, 4, -1) == ([0, 0, 0, 3, 3, 3, 6, 6], [2, 2, 2, 5, 5, 5, 7, 7])
+    assert _plan(host, c4, 8, -1) == _plan(host, c4, 4, -1)
+    assert _plan(host, c4, 8, -1, growth=1.0) == _plan(host, c4, 2, -1)
+    assert _plan(host, c4, 8, 0) == (list(range(8)), list(range(8)))
+    assert _plan(host, c4, 1, -1) == (list(range(8)), list(range(8)))
+    assert _plan(host, c4, 8, -1, allreduce=0) == (list(range(8)), list(range(8)))
+    assert _plan(host, c4, 8, 256) == ([0, 0, 0, 0, 4, 4, 4, 4], [3, 3, 3, 3, 7, 7, 7, 7])
+    # the deep narrow model: 20 one-MiB layers, a quarter is 5 MiB
+    low, high = _plan(host, [mib] * 20, 2, -1)
+    assert sorted(set(zip(low, high))) == [(0, 4), (5, 9), (10, 14), (15, 19)]
+    # the 4 MiB floor: 8 layers of 256 KiB make one bucket
+    low, high = _plan(host, [mib // 4] * 8, 2, -1)
+    assert set(zip(low, high)) == {(0, 7)}
+    # ragged widths: consecutive, covering, ordered
+    rag = [3 * mib, 70 * mib, mib, 9 * mib, 40 * mib]
+    for world in (2, 4, 8):
+        low, high = _plan(host, rag, world, -1)
+        for l in range(len(rag)):
+            assert low[l] <= l <= high[l]
+            assert all(low[k] == low[l] and high[k] == high[l] for k in range(low[l], high[l] + 1))
+
+
+def test_bench_reads_the_same_bucket_rule(host):
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("bench", os.path.join(os.path.dirname(__file__), "..", "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    mib = 1 << 20
+    assert bench.gradient_buckets([64 * mib] * 8, 2, -1) == [128 * mib] * 4
+    assert bench.gradient_buckets([64 * mib] * 8, 4, -1) == [128 * mib, 192 * mib, 192 * mib]
+    assert bench.gradient_buckets([64 * mib] * 8, 8, 0) == [64 * mib] * 8
