@@ -462,8 +462,8 @@ def main():
     sgd_bytes = n_params * (14 if args.precision == "bf16" else 12)
     sgd_gbs = sgd_bytes / (per_phase["sgd_ms"] / 1e3) / 1e9 if per_phase["sgd_ms"] > 0 else 0.0
     # DRAM bytes per GEMM launch (read + write) from an ncu capture of this kernel at
-    # 8192 x 4096 x 4096 bf16 (mean of a forward with ReLU, and a weight-gradient launch:
-    # profiles/gemm_tc_kernel_8192x4096x4096_bf16_ncu_full.md); other shapes were not captured
+    # 8192 x 4096 x 4096 bf16 (mean of two forward launches and a weight-gradient launch; the
+    # summary of that capture is kept under profiles/); other shapes were not captured
     traffic = None
     if args.precision == "bf16" and bl == 8192 and all(f == 4096 for f in nf):
         traffic = (192.8e6 + 41.8e6 + 213.7e6 + 87.2e6 + 237.6e6 + 42.4e6) / 3

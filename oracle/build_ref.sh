@@ -9,8 +9,8 @@
 #                                  counts), used to time the reference's CPU path on
 #                                  the benchmark configurations
 #
-# The reference sources are compiled from where they lie ($REF, default
-# /root/reference); nothing of them is written into the repository.  The patched
+# The reference sources are compiled from where they lie (the directory named by
+# $REF); nothing of them is written into the repository.  The patched
 # variants are produced in a temporary directory that is removed afterwards.
 # Without $REF only liboracle.so is built (the _ref binaries then have to be the
 # prebuilt ones).

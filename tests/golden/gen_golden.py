@@ -1,6 +1,6 @@
 """Regenerates the golden fixtures of this directory from the UNMODIFIED reference.
 
-Needs the reference sources (default /root/reference) and oracle/_ref built by
+Needs the reference sources (where oracle/build_ref.sh finds them) and oracle/_ref built by
 oracle/build_ref.sh; run once, commit the outputs:
 
     python tests/golden/gen_golden.py
