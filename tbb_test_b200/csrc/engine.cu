@@ -538,10 +538,16 @@ int b2_create(const b2_config* cfg, b2_handle** out) {
     if (cfg->nfeatures[i] < 1) return fail(nullptr, B2_ERR_INVALID, "nfeatures[%d] must be positive", i);
   if (cfg->world_size > 1 && cfg->allreduce && !cfg->nccl_unique_id)
     return fail(nullptr, B2_ERR_INVALID, "world_size > 1 needs nccl_unique_id");
-  // A captured step that contains collectives did not complete on two GPUs (cause not found);
-  // graph replay is for the latency-bound single-GPU configurations.
-  if (cfg->use_graph && cfg->world_size > 1 && cfg->allreduce)
-    return fail(nullptr, B2_ERR_UNSUPPORTED, "use_graph is not supported together with the gradient allreduce");
+  // A captured step that contains collectives did not complete on two GPUs. Probable cause: the
+  // communicator's first collective was issued under stream capture, while NCCL connects its
+  // channels lazily at the first collective of each kind. b2_step now issues every bucket's
+  // collective once, uncaptured, before it captures; until that has been confirmed on GPUs the
+  // combination stays refused unless B2_GRAPH_WITH_ALLREDUCE=1 is set.
+  if (cfg->use_graph && cfg->world_size > 1 && cfg->allreduce) {
+    const char* e = getenv("B2_GRAPH_WITH_ALLREDUCE");
+    if (!(e && e[0] == '1'))
+      return fail(nullptr, B2_ERR_UNSUPPORTED, "use_graph is not supported together with the gradient allreduce");
+  }
 
   int ndev = 0;
   cudaError_t e = cudaGetDeviceCount(&ndev);
@@ -897,6 +903,13 @@ int b2_step(b2_handle* h, int iters) {
     CK(h, cudaStreamSynchronize(h->s_main));
     CK(h, cudaStreamSynchronize(h->s_comm));
     CK(h, cudaStreamSynchronize(h->s_upd));
+    if (h->comm) {
+      // connect the communicator outside the capture: each bucket's collective once, in place on
+      // the gradient slab, whose contents are dead until the step's weight-gradient GEMMs rewrite them
+      for (int l = h->L - 1; l >= 0; --l)
+        if (h->bucket_low[l] == l && (rc = bucket_allreduce(h, l, h->bucket_high[l], h->s_comm, false))) return rc;
+      CK(h, cudaStreamSynchronize(h->s_comm));
+    }
     if ((rc = capture_graph(h))) return rc;
   }
   if (timed) {  // one event pair per (step, layer, phase): nothing is read back before the end
