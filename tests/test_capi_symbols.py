@@ -48,6 +48,25 @@ def test_create_fails_loudly_without_a_device(native):
     assert "no CPU path" in str(e.value)
 
 
+def test_argument_errors_come_before_any_device_work(native, monkeypatch):
+    """Bad configurations are refused with their own codes (no GPU needed to see them),
+    among them graph replay together with the gradient allreduce."""
+    from tbb_test_b200 import _capi as K
+    from tbb_test_b200.mlp import MLP
+    monkeypatch.delenv("B2_GRAPH_WITH_ALLREDUCE", raising=False)
+    with pytest.raises(K.B2Error) as e:
+        MLP([16, 16], 8, world_size=2, rank=0, nccl_id=b"\0" * K.NCCL_ID_BYTES, use_graph=True)
+    assert e.value.code == K.ERR_UNSUPPORTED and "use_graph" in str(e.value)
+    for kw in (dict(world_size=2, rank=2, nccl_id=b"\0" * K.NCCL_ID_BYTES), dict(world_size=2, rank=0),
+               dict(grad_bf16=True, precision=K.PREC_FP32)):
+        with pytest.raises(K.B2Error) as e:
+            MLP([16, 16], 8, **kw)
+        assert e.value.code == K.ERR_INVALID, kw
+    with pytest.raises(K.B2Error) as e:
+        MLP([16, 0], 8)
+    assert e.value.code == K.ERR_INVALID
+
+
 def test_product_does_not_import_the_oracle():
     """The oracle is test infrastructure: nothing in the package may reach for it."""
     pkg = os.path.join(ROOT, "tbb_test_b200")
