@@ -221,6 +221,27 @@ int b2_allreduce_sgd(b2_handle* h, int layer);
 int b2_allreduce_bench(b2_handle* h, size_t count, int dtype, int warmup, int iters,
                        double* ms_per_iter, double* checksum);
 
+/* Peer-memory path for small gradient messages (the 1 MiB layers of the deep narrow
+ * configuration, where a library collective is latency-bound). The reference moves its
+ * gradients between sockets by plain loads and stores to the other sockets' buffers
+ * (mlp_omp.cc:94-160); this is the same idea between GPUs over NVLink: each rank sums the
+ * chunk it owns straight out of every rank's gradient buffer, in rank order, and stores the
+ * sum into every rank's buffer, with two bounded flag exchanges per call.
+ *   1. every rank: b2_p2p_describe(h, desc)            B2_P2P_DESC_BYTES bytes
+ *   2. exchange the descriptors between the ranks (threads: an array; processes: any transport)
+ *   3. every rank: b2_p2p_connect(h, all_descs, max_bytes) with all_descs in rank order
+ * From then on gradient sums of at most max_bytes (fp32 gradients, no graph replay) bypass
+ * NCCL; larger ones still use it. All ranks must pass the same max_bytes, and none may destroy
+ * its handle while another still runs steps. A rank that waits longer than a second for
+ * another gets B2_ERR_TIMEOUT from its next synchronising call and falls back to NCCL-only. */
+#define B2_P2P_DESC_BYTES 128
+int b2_p2p_describe(b2_handle* h, void* desc);
+int b2_p2p_connect(b2_handle* h, const void* descs, size_t max_bytes);
+/* The same kernel with all `world` ranks emulated on ONE GPU (one cooperative launch; for
+ * machines with fewer GPUs than ranks): bufs[r] = rank r's `count` host floats, replaced by the
+ * sum over ranks. No handle needed. The reference has no counterpart. */
+int b2_p2p_emulate(int device, int world, float* const* bufs, size_t count);
+
 /* Device times in milliseconds accumulated since the last reset:
  * phase_ms[l * B2_T_NUM + phase] per layer (needs collect_timing), and
  * *step_ms / *steps for whole steps (always collected). Feeds report_timing

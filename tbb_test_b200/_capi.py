@@ -17,6 +17,7 @@ DTYPE_F32, DTYPE_BF16 = 0, 1
 EPI_NONE, EPI_RELU, EPI_MASK = 0, 1, 2
 T_FWD, T_WGT_GRAD, T_BWD, T_WGT_UPDATE, T_ALLREDUCE, T_NUM = 0, 1, 2, 3, 4, 5
 NCCL_ID_BYTES = 128
+P2P_DESC_BYTES = 128
 NOALLOC_MAX_OPERAND_ELEMS = 4 * 1024 * 1024
 
 _fp = C.POINTER(C.c_float)
@@ -70,6 +71,9 @@ SYMBOLS = {
     "b2_noalloc_last_error": (C.c_char_p, []),
     "b2_allreduce_sgd": (C.c_int, [_H, C.c_int]),
     "b2_allreduce_bench": (C.c_int, [_H, C.c_size_t, C.c_int, C.c_int, C.c_int, _dp, _dp]),
+    "b2_p2p_describe": (C.c_int, [_H, C.c_void_p]),
+    "b2_p2p_connect": (C.c_int, [_H, C.c_void_p, C.c_size_t]),
+    "b2_p2p_emulate": (C.c_int, [C.c_int, C.c_int, C.POINTER(_fp), C.c_size_t]),
     "b2_get_timing": (C.c_int, [_H, _dp, _dp, C.POINTER(C.c_longlong)]),
     "b2_get_gemm_busy_ms": (C.c_int, [_H, _dp]),
     "b2_reset_timing": (C.c_int, [_H]),

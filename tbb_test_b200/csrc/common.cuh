@@ -54,6 +54,30 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
 void gemm_tc_plan_destroy(TcPlan* p);
 cudaError_t gemm_tc_launch(const TcPlan* p, cudaStream_t stream, unsigned int* status);
 
+// Small-message allreduce over peer memory (p2p_allreduce.cu). Every rank's gradient slab and
+// flag block are addressable from every rank (peer access within a process, IPC mappings
+// between processes). A flag block is 2 * P2P_MAX_RANKS words, written by the peers: word
+// P2P_FLAG_ARRIVE + r = "rank r's input of call `epoch` is ready", P2P_FLAG_DONE + r = "rank r's
+// stores of call `epoch` are done".
+constexpr int P2P_MAX_RANKS = 8;
+constexpr int P2P_FLAG_ARRIVE = 0;
+constexpr int P2P_FLAG_DONE = P2P_MAX_RANKS;
+constexpr size_t P2P_FLAG_BYTES = 2 * P2P_MAX_RANKS * sizeof(unsigned int);
+struct P2pParams {
+  float* slab[P2P_MAX_RANKS];          // index = rank; slab[rank] is this rank's own
+  unsigned int* flags[P2P_MAX_RANKS];  // index = rank
+  int world, rank;
+  unsigned long long offset;  // first element of the message in every slab (multiple of 4)
+  unsigned long long count;   // elements
+  unsigned int epoch;         // call counter, > 0, the same on every rank for the same call
+  unsigned int* ctas_done;    // this rank's own counter, zero between calls
+  unsigned int* status;       // this rank's own word, set non-zero when a wait gave up
+};
+// One rank's launch (every rank launches its own, each on its own GPU).
+cudaError_t p2p_allreduce_launch(const P2pParams& p, int cta_limit, cudaStream_t stream);
+// All ranks in one cooperative launch on one GPU: `ranks_dev` = device array of world entries.
+cudaError_t p2p_allreduce_emulated_launch(const P2pParams* ranks_dev, const P2pParams& any_rank, cudaStream_t stream);
+
 // Element-wise kernels.
 cudaError_t convert_f32_to_bf16(const float* src, __nv_bfloat16* dst, size_t n, cudaStream_t s);
 cudaError_t convert_bf16_to_f32(const __nv_bfloat16* src, float* dst, size_t n, cudaStream_t s);

@@ -14,6 +14,7 @@
 // by dedicating threads: mlp_omp.cc:520-527,601-615,692-723).
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <unistd.h>
 
 #include <algorithm>
 #include <cstdarg>
@@ -64,6 +65,16 @@ struct b2_handle {
   // All weight gradients live in one slab, last layer first (the order backward produces
   // them), so that consecutive layers can be summed by one collective call ("bucket").
   void* dw_slab = nullptr;
+  // Peer-memory path for small gradient messages (b2_p2p_connect): every rank's slab and the
+  // flag block at its end are mapped here; messages up to p2p_max_bytes bypass NCCL.
+  size_t slab_bytes = 0, p2p_flags_off = 0;
+  bool p2p_ready = false;
+  size_t p2p_max_bytes = 0;
+  unsigned int p2p_epoch = 0;
+  unsigned int* p2p_ctas_done = nullptr;
+  float* p2p_slab[P2P_MAX_RANKS] = {};
+  unsigned int* p2p_flags[P2P_MAX_RANKS] = {};
+  void* p2p_opened[P2P_MAX_RANKS] = {};  // IPC mappings of other processes' slabs
   std::vector<size_t> dw_off;       // element offset of dw[l] in the slab
   std::vector<int> bucket_low;      // for layer l: lowest layer index of its bucket
   std::vector<int> bucket_high;     // for layer l: highest layer index of its bucket
@@ -182,6 +193,12 @@ int check_status(b2_handle* h) {
   if (st != 0) {
     cudaMemset(h->status_dev, 0, sizeof st);
     if (h->tc_ws_flags) cudaMemset(h->tc_ws_flags, 0, (size_t)h->sms * sizeof(unsigned int));
+    if (st >= 100u) {  // a flag wait of the peer-memory allreduce: its call counters no longer agree
+      h->p2p_ready = false;
+      cudaMemset(h->p2p_ctas_done, 0, sizeof(unsigned int));
+      return fail(h, B2_ERR_TIMEOUT, "peer-memory allreduce gave up waiting for another rank (code %u); "
+                  "the peer path is switched off for this handle", st);
+    }
     return fail(h, B2_ERR_TIMEOUT, "tensor-core GEMM gave up waiting on a pipeline barrier (role %u)", st);
   }
   return B2_OK;
@@ -294,12 +311,39 @@ int build_sites(b2_handle* h) {
   return B2_OK;
 }
 
+// Sum of `count` gradient elements starting `begin` elements into the slab, over all ranks:
+// through peer memory when the ranks are connected and the message is small, else NCCL.
+int sum_gradients(b2_handle* h, size_t begin, size_t count, cudaStream_t st) {
+  const size_t es = esize(h->grad_type);
+  if (h->p2p_ready && h->grad_type == T_F32 && !h->cfg.use_graph && count * es <= h->p2p_max_bytes) {
+    P2pParams p{};
+    for (int r = 0; r < h->cfg.world_size; ++r) {
+      p.slab[r] = h->p2p_slab[r];
+      p.flags[r] = h->p2p_flags[r];
+    }
+    p.world = h->cfg.world_size;
+    p.rank = h->cfg.rank;
+    p.offset = begin;
+    p.count = count;
+    p.epoch = ++h->p2p_epoch;
+    p.ctas_done = h->p2p_ctas_done;
+    p.status = h->status_dev;
+    ++h->launches;
+    CK(h, p2p_allreduce_launch(p, h->cfg.comm_sms, st));
+    return B2_OK;
+  }
+  char* base = static_cast<char*>(h->dw_slab) + begin * es;
+  NCK(h, nccl_api().AllReduce(base, base, count, h->grad_type == T_BF16 ? ncclBfloat16 : ncclFloat32, ncclSum,
+                              h->comm, st));
+  return B2_OK;
+}
+
 int layer_update(b2_handle* h, int l, cudaStream_t st, bool timed) {
   const size_t n = (size_t)h->nf[l + 1] * h->nf[l];
   if (h->cfg.world_size > 1 && h->cfg.allreduce) {
     if (timed) CK(h, cudaEventRecord(phase_ev(h, l, B2_T_ALLREDUCE, 0), st));
-    NCK(h, nccl_api().AllReduce(h->dw[l], h->dw[l], n, h->grad_type == T_BF16 ? ncclBfloat16 : ncclFloat32,
-                                ncclSum, h->comm, st));
+    int rc = sum_gradients(h, h->dw_off[l], n, st);
+    if (rc) return rc;
     if (timed) CK(h, cudaEventRecord(phase_ev(h, l, B2_T_ALLREDUCE, 1), st));
   }
   return B2_OK;
@@ -310,10 +354,9 @@ int bucket_allreduce(b2_handle* h, int low, int high, cudaStream_t st, bool time
   if (!(h->cfg.world_size > 1 && h->cfg.allreduce)) return B2_OK;
   const size_t begin = h->dw_off[high];
   const size_t end = h->dw_off[low] + (size_t)h->nf[low + 1] * h->nf[low];
-  char* base = static_cast<char*>(h->dw_slab) + begin * esize(h->grad_type);
   if (timed) CK(h, cudaEventRecord(phase_ev(h, low, B2_T_ALLREDUCE, 0), st));
-  NCK(h, nccl_api().AllReduce(base, base, end - begin, h->grad_type == T_BF16 ? ncclBfloat16 : ncclFloat32, ncclSum,
-                              h->comm, st));
+  int rc = sum_gradients(h, begin, end - begin, st);
+  if (rc) return rc;
   if (timed) CK(h, cudaEventRecord(phase_ev(h, low, B2_T_ALLREDUCE, 1), st));
   return B2_OK;
 }
@@ -441,6 +484,9 @@ void free_all(b2_handle* h) {
   for (auto& s : h->dgrad) gemm_tc_plan_destroy(s.plan);
   for (auto p : h->w) cudaFree(p);
   for (auto p : h->w16) cudaFree(p);
+  for (int r = 0; r < P2P_MAX_RANKS; ++r)
+    if (h->p2p_opened[r]) cudaIpcCloseMemHandle(h->p2p_opened[r]);
+  cudaFree(h->p2p_ctas_done);
   cudaFree(h->dw_slab);
   for (auto p : h->act) cudaFree(p);
   for (auto p : h->dz) cudaFree(p);
@@ -646,7 +692,10 @@ int b2_create(const b2_config* cfg, b2_handle** out) {
       const size_t nw = (size_t)h->nf[l + 1] * h->nf[l];
       total += (nw + align_elems - 1) / align_elems * align_elems;
     }
-    TRY(dev_alloc(h, &h->dw_slab, total * es));
+    h->p2p_flags_off = (total * es + 255) / 256 * 256;
+    h->slab_bytes = h->p2p_flags_off + 256;  // zero-filled flag block (P2P_FLAG_BYTES) behind the gradients
+    TRY(dev_alloc(h, &h->dw_slab, h->slab_bytes));
+    TRY(dev_alloc(h, &h->p2p_ctas_done, sizeof(unsigned int)));
     for (int l = 0; l < L; ++l) h->dw[l] = static_cast<char*>(h->dw_slab) + h->dw_off[l] * es;
     // buckets of consecutive layers (rule and rationale: bucket_plan.h); B2_BUCKET_GROWTH
     // overrides the factor between consecutive buckets
@@ -1074,6 +1123,136 @@ int b2_allreduce_sgd(b2_handle* h, int l) {
   if ((rc = layer_sgd(h, l, h->s_main, false))) return rc;
   CK(h, cudaStreamSynchronize(h->s_main));
   return B2_OK;
+}
+
+namespace {
+// What b2_p2p_describe writes: where this rank's gradient slab lives and how to map it.
+struct P2pDesc {
+  uint32_t magic;
+  int32_t device;
+  int64_t pid;
+  uint64_t ptr, slab_bytes, flags_off;
+  cudaIpcMemHandle_t ipc;
+};
+static_assert(sizeof(P2pDesc) <= B2_P2P_DESC_BYTES, "descriptor does not fit");
+constexpr uint32_t P2P_MAGIC = 0x62327032u;
+}  // namespace
+
+int b2_p2p_describe(b2_handle* h, void* desc) {
+  ENTER(h);
+  if (!desc) return fail(h, B2_ERR_INVALID, "null descriptor");
+  if (h->cfg.world_size < 2 || h->cfg.world_size > P2P_MAX_RANKS)
+    return fail(h, B2_ERR_UNSUPPORTED, "the peer-memory path serves 2 to %d ranks", P2P_MAX_RANKS);
+  if (h->grad_type != T_F32) return fail(h, B2_ERR_UNSUPPORTED, "the peer-memory path sums fp32 gradients only");
+  P2pDesc d;
+  memset(&d, 0, sizeof d);
+  d.magic = P2P_MAGIC;
+  d.device = h->cfg.device;
+  d.pid = (int64_t)getpid();
+  d.ptr = (uint64_t)(uintptr_t)h->dw_slab;
+  d.slab_bytes = h->slab_bytes;
+  d.flags_off = h->p2p_flags_off;
+  CK(h, cudaIpcGetMemHandle(&d.ipc, h->dw_slab));
+  memset(desc, 0, B2_P2P_DESC_BYTES);
+  memcpy(desc, &d, sizeof d);
+  return B2_OK;
+}
+
+int b2_p2p_connect(b2_handle* h, const void* descs, size_t max_bytes) {
+  ENTER(h);
+  if (!descs) return fail(h, B2_ERR_INVALID, "null descriptors");
+  if (h->p2p_ready) return fail(h, B2_ERR_STATE, "already connected");
+  const int world = h->cfg.world_size, rank = h->cfg.rank;
+  if (world < 2 || world > P2P_MAX_RANKS)
+    return fail(h, B2_ERR_UNSUPPORTED, "the peer-memory path serves 2 to %d ranks", P2P_MAX_RANKS);
+  if (h->grad_type != T_F32) return fail(h, B2_ERR_UNSUPPORTED, "the peer-memory path sums fp32 gradients only");
+  for (int r = 0; r < world; ++r) {
+    P2pDesc d;
+    memcpy(&d, static_cast<const char*>(descs) + (size_t)r * B2_P2P_DESC_BYTES, sizeof d);
+    if (d.magic != P2P_MAGIC) return fail(h, B2_ERR_INVALID, "descriptor %d is not one of b2_p2p_describe", r);
+    if (d.slab_bytes != h->slab_bytes || d.flags_off != h->p2p_flags_off)
+      return fail(h, B2_ERR_INVALID, "rank %d was created for a different model", r);
+    char* base = nullptr;
+    if (r == rank) {
+      if (d.ptr != (uint64_t)(uintptr_t)h->dw_slab) return fail(h, B2_ERR_INVALID, "descriptor %d is not this rank's", r);
+      base = static_cast<char*>(h->dw_slab);
+    } else if (d.pid == (int64_t)getpid()) {
+      // another handle of this process: its pointer is valid here once peer access is on
+      if (d.device != h->cfg.device) {
+        int can = 0;
+        CK(h, cudaDeviceCanAccessPeer(&can, h->cfg.device, d.device));
+        if (!can) return fail(h, B2_ERR_UNSUPPORTED, "device %d cannot access device %d", h->cfg.device, d.device);
+        cudaError_t e = cudaDeviceEnablePeerAccess(d.device, 0);
+        if (e == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
+        else if (e != cudaSuccess) return fail(h, B2_ERR_CUDA, "cudaDeviceEnablePeerAccess: %s", cudaGetErrorString(e));
+      }
+      base = reinterpret_cast<char*>((uintptr_t)d.ptr);
+    } else {
+      void* mapped = nullptr;
+      CK(h, cudaIpcOpenMemHandle(&mapped, d.ipc, cudaIpcMemLazyEnablePeerAccess));
+      h->p2p_opened[r] = mapped;
+      base = static_cast<char*>(mapped);
+    }
+    h->p2p_slab[r] = reinterpret_cast<float*>(base);
+    h->p2p_flags[r] = reinterpret_cast<unsigned int*>(base + h->p2p_flags_off);
+  }
+  h->p2p_max_bytes = max_bytes;
+  h->p2p_epoch = 0;
+  h->p2p_ready = max_bytes > 0;
+  return B2_OK;
+}
+
+int b2_p2p_emulate(int device, int world, float* const* bufs, size_t count) {
+  if (world < 2 || world > P2P_MAX_RANKS || !bufs || count == 0)
+    return fail(nullptr, B2_ERR_INVALID, "bad arguments");
+  cudaError_t e = cudaSetDevice(device);
+  if (e != cudaSuccess) return fail(nullptr, B2_ERR_CUDA, "cudaSetDevice: %s", cudaGetErrorString(e));
+  // one allocation: world slabs (count floats, padded) + world flag blocks + counters + status + parameters
+  const size_t slab = (count * sizeof(float) + 255) / 256 * 256;
+  const size_t off_flags = slab * world, off_cnt = off_flags + 256 * (size_t)world;
+  const size_t off_status = off_cnt + 256, off_params = off_status + 256;
+  const size_t total = off_params + sizeof(P2pParams) * world;
+  char* mem = nullptr;
+  unsigned int status = 0;
+  int rc = B2_OK;
+  P2pParams host[P2P_MAX_RANKS];
+  if ((e = cudaMalloc((void**)&mem, total)) != cudaSuccess)
+    return fail(nullptr, B2_ERR_CUDA, "cudaMalloc: %s", cudaGetErrorString(e));
+  do {
+    if ((e = cudaMemset(mem, 0, total)) != cudaSuccess) break;
+    for (int r = 0; r < world; ++r) {
+      if ((e = cudaMemcpy(mem + slab * r, bufs[r], count * sizeof(float), cudaMemcpyHostToDevice)) != cudaSuccess) break;
+      P2pParams& p = host[r];
+      memset(&p, 0, sizeof p);
+      for (int q = 0; q < world; ++q) {
+        p.slab[q] = reinterpret_cast<float*>(mem + slab * q);
+        p.flags[q] = reinterpret_cast<unsigned int*>(mem + off_flags + 256 * (size_t)q);
+      }
+      p.world = world;
+      p.rank = r;
+      p.offset = 0;
+      p.count = count;
+      p.epoch = 1;
+      p.ctas_done = reinterpret_cast<unsigned int*>(mem + off_cnt) + r;
+      p.status = reinterpret_cast<unsigned int*>(mem + off_status);
+    }
+    if (e != cudaSuccess) break;
+    if ((e = cudaMemcpy(mem + off_params, host, sizeof(P2pParams) * world, cudaMemcpyHostToDevice)) != cudaSuccess) break;
+    if ((e = p2p_allreduce_emulated_launch(reinterpret_cast<const P2pParams*>(mem + off_params), host[0], 0)) !=
+        cudaSuccess)
+      break;
+    if ((e = cudaDeviceSynchronize()) != cudaSuccess) break;
+    if ((e = cudaMemcpy(&status, mem + off_status, sizeof status, cudaMemcpyDeviceToHost)) != cudaSuccess) break;
+    if (status != 0) {
+      rc = fail(nullptr, B2_ERR_TIMEOUT, "emulated ranks gave up waiting for one another (code %u)", status);
+      break;
+    }
+    for (int r = 0; r < world && e == cudaSuccess; ++r)
+      e = cudaMemcpy(bufs[r], mem + slab * r, count * sizeof(float), cudaMemcpyDeviceToHost);
+  } while (0);
+  cudaFree(mem);
+  if (e != cudaSuccess) return fail(nullptr, B2_ERR_CUDA, "peer-allreduce emulation: %s", cudaGetErrorString(e));
+  return rc;
 }
 
 int b2_allreduce_bench(b2_handle* h, size_t count, int dtype, int warmup, int iters, double* ms_per_iter,

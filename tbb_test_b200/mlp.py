@@ -27,6 +27,17 @@ def nccl_unique_id():
     return bytes(buf)
 
 
+def p2p_emulate(bufs, device=0):
+    """Sum of the equally long float32 arrays `bufs` (one per emulated rank) into each of them,
+    by the peer-memory allreduce kernel with all ranks on one GPU."""
+    arrs = [np.ascontiguousarray(b, dtype=np.float32) for b in bufs]
+    ptrs = (_fp * len(arrs))(*[a.ctypes.data_as(_fp) for a in arrs])
+    rc = K.lib().b2_p2p_emulate(device, len(arrs), ptrs, arrs[0].size)
+    if rc != K.OK:
+        raise K.B2Error(rc, K.lib().b2_last_error(None).decode())
+    return arrs
+
+
 class MLP:
     def __init__(self, nfeatures, batch, *, rank=0, world_size=1, device=0, mode=K.MODE_BASELINE,
                  precision=K.PREC_FP32, grad_bf16=False, allreduce=True, overlap=True, input_grad=True,
@@ -185,6 +196,18 @@ class MLP:
         ms, cs = C.c_double(), C.c_double()
         self._ck(self.lib.b2_allreduce_bench(self._h, count, dtype, warmup, iters, C.byref(ms), C.byref(cs)))
         return ms.value, cs.value
+
+    # -- peer-memory path for small gradient messages ------------------------
+    def p2p_describe(self):
+        buf = (C.c_char * K.P2P_DESC_BYTES)()
+        self._ck(self.lib.b2_p2p_describe(self._h, buf))
+        return bytes(buf)
+
+    def p2p_connect(self, descs, max_bytes):
+        """descs: every rank's p2p_describe() bytes, in rank order."""
+        blob = b"".join(descs)
+        buf = C.create_string_buffer(blob, len(blob))
+        self._ck(self.lib.b2_p2p_connect(self._h, buf, max_bytes))
 
     # -- metrics ----------------------------------------------------------
     def timing(self):

@@ -46,6 +46,47 @@ def main():
     assert abs(checksum - ref) <= 1e-3, (checksum, ref)
     dev.close()
 
+    # 1b. the same known-answer test and a few steps of the deep narrow shape through the
+    # peer-memory path (gradient sums of up to 4 MiB bypass NCCL), against the NCCL path
+    if os.environ.get("B2_TEST_P2P") == "1":
+        def connected(dev):
+            descs = [None] * world
+            dist.all_gather_object(descs, dev.p2p_describe())
+            dev.p2p_connect(descs, 4 << 20)
+            dist.barrier()
+            return dev
+
+        dev = connected(MLP([ncols, nrows], 8 * world, rank=rank, world_size=world, device=local, lr=1.0,
+                            nccl_id=fresh_id()))
+        dev.upload_weights(0, w[rank])
+        dev.upload_weight_grad(0, g[rank])
+        dev.update_weight(0)
+        assert np.array_equal(dev.weights(0), e), f"rank {rank}: known-answer test through peer memory failed"
+        dist.barrier()
+        dev.close()
+        nf_s, batch_s = [128, 512, 512, 64], 64 * world + 3
+        ws_s, x_s, t_s = make_problem(O, nf_s, batch_s)
+        results = []
+        for p2p in (False, True):
+            dev = MLP(nf_s, batch_s, rank=rank, world_size=world, device=local, precision=K.PREC_FP32, lr=0.01,
+                      nccl_id=fresh_id(), ar_bucket_mb=0)
+            if p2p:
+                connected(dev)
+            for l in range(3):
+                dev.upload_weights(l, ws_s[l])
+            dev.upload_input(x_s)
+            dev.upload_target(t_s)
+            dev.step(4)
+            results.append([dev.weights(l) for l in range(3)] + [dev.weight_grad(l) for l in range(3)])
+            dist.barrier()
+            dev.close()
+        for a, b in zip(*results):  # same sums, possibly in another order
+            assert rel_fro(b, a) <= 1e-6
+        # every rank holds identical weights after the peer-memory steps
+        box = [None] * world
+        dist.all_gather_object(box, [float(np.float64(x).sum()) for x in results[1][:3]])
+        assert all(b == box[0] for b in box)
+
     # 2. training steps: every precision, ragged batch split, against the oracle with `world` ranks
     nf, batch, steps = [256, 512, 256, 128], 200 + world, 3
     ws, x, t = make_problem(O, nf, batch)
