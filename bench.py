@@ -323,6 +323,8 @@ def main():
     ap.add_argument("--bucket-mb", type=int, default=-1,
                     help="gradient allreduce granularity in MiB (0 = per layer, -1 = library default)")
     ap.add_argument("--grad-bf16", action="store_true", help="bf16 weight gradients (configuration 5 style)")
+    ap.add_argument("--p2p-bytes", type=int, default=0,
+                    help="gradient sums up to this many bytes go through peer memory instead of NCCL (0 = off)")
     ap.add_argument("--trace", default=None,
                     help="write rank 0's Chrome trace (per-kernel intervals of the timed steps) to this file")
     ap.add_argument("--graph", action="store_true",
@@ -411,6 +413,11 @@ def main():
               lr=0.01, nccl_id=nccl_id, collect_timing=not args.graph, use_graph=args.graph,
               comm_sms=args.comm_sms, grad_bf16=args.grad_bf16, ar_bucket_mb=args.bucket_mb)
     b0, b1 = dev.rows
+    if args.p2p_bytes > 0 and world > 1:
+        descs = [None] * world
+        dist.all_gather_object(descs, dev.p2p_describe())
+        dev.p2p_connect(descs, args.p2p_bytes)
+        dist.barrier()
 
     # seeded synthetic data (weights seed 0, inputs seed 1, targets seed 2); every rank
     # draws the same weights and only its own rows of the batch
