@@ -11,6 +11,7 @@
 //     --precision fp32|tf32|bf16                          (default bf16)
 //     --mode ref|baseline                                 (default ref, lr 1e-10)
 //     --lr X   --warmup N   --iters N   --no-overlap   --no-allreduce   --graph
+//     --p2p-bytes N            gradient sums up to N bytes through peer memory instead of NCCL
 #include <atomic>
 #include <chrono>
 #include <cmath>
@@ -36,6 +37,7 @@ struct Options {
   float lr = 1e-10f;
   int warmup = 16, iters = 256;
   int overlap = 1, allreduce = 1, graph = 0;
+  long long p2p_bytes = 0;
 };
 
 bool parse(int argc, char** argv, Options* o) {
@@ -70,6 +72,7 @@ bool parse(int argc, char** argv, Options* o) {
     else if (a == "--no-overlap") o->overlap = 0;
     else if (a == "--no-allreduce") o->allreduce = 0;
     else if (a == "--graph") o->graph = 1;
+    else if (a == "--p2p-bytes") o->p2p_bytes = atoll(next());
     else return false;
   }
   if (o->batch <= 0) o->batch = 1024 * o->ngpus;  // weak scaling like the reference (mlp_omp.cc:386)
@@ -150,7 +153,8 @@ int main(int argc, char** argv) {
   if (!parse(argc, argv, &o)) {
     fprintf(stderr,
             "%s <ngpus> [<nthreads_per_socket>] [--widths a,b,..] [--batch N] [--precision fp32|tf32|bf16]\n"
-            "        [--mode ref|baseline] [--lr X] [--warmup N] [--iters N] [--no-overlap] [--no-allreduce] [--graph]\n",
+            "        [--mode ref|baseline] [--lr X] [--warmup N] [--iters N] [--no-overlap] [--no-allreduce] [--graph]\n"
+            "        [--p2p-bytes N]\n",
             argv[0]);
     return 1;
   }
@@ -199,6 +203,13 @@ int main(int argc, char** argv) {
     return rc;
   });
   if (!ok) return 2;
+  if (o.p2p_bytes > 0 && o.ngpus > 1 && o.allreduce) {
+    // every GPU's gradient buffer becomes addressable from every other GPU (one process: peer access)
+    std::vector<char> descs((size_t)o.ngpus * B2_P2P_DESC_BYTES);
+    ok = on_all_gpus(ws, [&](int g) -> int { return b2_p2p_describe(ws[g].h, &descs[(size_t)g * B2_P2P_DESC_BYTES]); }) &&
+         on_all_gpus(ws, [&](int g) -> int { return b2_p2p_connect(ws[g].h, descs.data(), (size_t)o.p2p_bytes); });
+    if (!ok) return 2;
+  }
 
   if (o.allreduce && !check_all_reduce_correctness(ws, o)) return -1;
 
