@@ -485,7 +485,10 @@ def main():
                         "note": "runs on the side stream concurrently with GEMMs"}}
     if world > 1 and per_phase["allreduce_ms"] > 0:
         ar_bytes = n_params * (2 if args.grad_bf16 else 4)
-        roofline["allreduce"] = {"busbw_gbs": ar_bytes * 2 * (world - 1) / world / (per_phase["allreduce_ms"] / 1e3) / 1e9,
+        busbw = ar_bytes * 2 * (world - 1) / world / (per_phase["allreduce_ms"] / 1e3) / 1e9
+        roofline["allreduce"] = {"bound": "nvlink", "busbw_gbs": busbw, "peak": 770.0, "unit": "GB/s",
+                                 "frac": busbw / 770.0,
+                                 "peak_source": "measured peer copy per direction on this pool (900 nominal)",
                                  "note": "gradient ncclAllReduce calls timed on the side stream while GEMMs run"}
         # How much of the allreduce hides behind compute: 1 - (t_step - t_step,no allreduce) / t_allreduce,alone
         # (the reference's NO_ALL_REDUCE build gives the middle term, mlp_omp.cc:21). The buckets are
@@ -516,7 +519,8 @@ def main():
         roofline["allreduce"].update({
             "alone_ms_per_step": t_alone, "buckets_bytes": buckets, "step_ms_without_allreduce": t_noar,
             "hidden_fraction": 1.0 - (ms_per_step - t_noar) / t_alone if t_alone > 0 else None,
-            "busbw_alone_gbs": sum(buckets) * 2 * (world - 1) / world / (t_alone / 1e3) / 1e9 if t_alone > 0 else None})
+            "busbw_alone_gbs": sum(buckets) * 2 * (world - 1) / world / (t_alone / 1e3) / 1e9 if t_alone > 0 else None,
+            "frac_alone": sum(buckets) * 2 * (world - 1) / world / (t_alone / 1e3) / 1e9 / 770.0 if t_alone > 0 else None})
 
     # ---- end to end through the host-facing call --------------------------------
     # Every step: this step's inputs and targets are copied from pinned host memory
