@@ -13,12 +13,19 @@ bf16 tensor-core operands with fp32 accumulation and fp32 master weights; with
 N GPUs the global batch is split evenly (strong scaling) and each layer's 64 MiB
 fp32 gradient is summed with NCCL on a side stream.
 
+kat       before anything is timed every rank runs the reference's own start-up
+          self-check (allreduce + SGD known-answer test, mlp_omp.cc:325-373) through
+          b2_allreduce_sgd; after the timed steps the ranks compare fingerprints of
+          their weights. A failed check ends the run with a non-zero exit code.
 value     global batch * K / device time of K steps (CUDA events on the launching
-          stream inside the library; max over ranks), inputs resident in HBM
-e2e       same metric through b2_train_step_host: every step copies that step's
-          inputs and targets from pinned host memory and reads the loss back
-roofline  the GEMMs: 2mnk flops of all GEMM launches / their summed event time,
-          against the measured cuBLAS bf16 peak of MEASURED_PEAKS.json
+          stream inside the library; max over ranks), inputs resident in HBM, no
+          per-phase events in the timed steps
+e2e       same metric through b2_train_step_host_async: every step copies that
+          step's inputs and targets from pinned host memory and reads the loss back
+roofline  the GEMMs: 2mnk flops of all GEMM launches / the time during which a GEMM
+          was running, from a second, shorter run with per-phase events, against the
+          measured cuBLAS bf16 peak of MEASURED_PEAKS.json (burst figure: the timed
+          region is well under a second; the sustained figure is quoted beside it)
 cpu_baseline / --impl reference
           the reference's own mlp_omp (oracle/_ref, built from the unmodified
           sources with only the workload literals replaced) timed on the host cores
@@ -109,15 +116,21 @@ def pick_sockets_threads(cores):
     return best
 
 
-def run_reference_cpu(workload, batch):
+REF_ITERS = {"c1": (3, 20), "c3": (3, 20), "c4": (1, 4)}  # most (warm-up, timed) steps a CPU sample may take
+
+
+def run_reference_cpu(workload, batch, warmup=None, steps=None):
     """Times oracle/_ref/mlp_omp_<workload> on the host cores. Returns a dict or None."""
     exe = os.path.join(ROOT, "oracle", "_ref", f"mlp_omp_{workload}")
     if not os.path.exists(exe) or not has_avx512():
         return None
     cores = host_cores()
     s, t = pick_sockets_threads(cores)
+    cap_w, cap_k = REF_ITERS.get(workload, (1, 2))
+    nwarm = max(1, min(cap_w, warmup if warmup is not None else cap_w))
+    niter = max(1, min(cap_k, steps if steps is not None else cap_k))
     env = dict(os.environ, OMP_PROC_BIND="close", OMP_PLACES="cores", OPENBLAS_NUM_THREADS="1",
-               OMP_NUM_THREADS=str(s * t))
+               OMP_NUM_THREADS=str(s * t), B2_REF_NWARMUP=str(nwarm), B2_REF_NITER=str(niter))
     t0 = time.time()
     try:
         r = subprocess.run([exe, str(s), str(t)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
@@ -128,11 +141,10 @@ def run_reference_cpu(workload, batch):
     if r.returncode != 0 or not m:
         return None
     ms = float(m.group(1))
-    it = {"c1": (2, 8), "c3": (2, 8), "c4": (1, 2)}[workload]
     return {"value": batch / (ms / 1e3), "ms_per_step": ms, "cores": s * t, "sockets": s, "kind": "reference",
-            "unit": "samples/s", "wall_s": round(time.time() - t0, 1),
+            "unit": "samples/s", "wall_s": round(time.time() - t0, 1), "steps": niter, "warmup": nwarm,
             "sample": f"unmodified mlp_omp built with this workload's widths/batch, {s} socket(s) x {t} threads, "
-                      f"OpenBLAS sgemm, {it[0]} warm-up + {it[1]} timed steps of the full workload"}
+                      f"OpenBLAS sgemm, {nwarm} warm-up + {niter} timed steps of the full workload"}
 
 
 def run_port_cpu(nf, batch, steps=1):
@@ -153,6 +165,7 @@ def run_port_cpu(nf, batch, steps=1):
     dt = (time.time() - t0) / steps
     O.use_builtin_gemm()
     return {"value": rows / dt, "ms_per_step": dt * 1e3, "cores": cores, "kind": "port", "unit": "samples/s",
+            "steps": steps, "warmup": 1,
             "sample": f"oracle port (OpenBLAS, {cores} threads) on a {rows}-row slice of the batch, {steps} step(s)"}
 
 
@@ -208,6 +221,27 @@ def measured_peaks():
         return p, "measured"
     except Exception:
         return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+def profiled_traffic(precision, rows, nf):
+    """DRAM bytes (read + write) per GEMM launch from the ncu summary kept for this shape under
+    profiles/ (a line `dram_bytes_per_launch: fwd=.. wgrad=.. dgrad=..`), mean over the three
+    forms, or None when the shape was not profiled."""
+    if not all(f == nf[0] for f in nf):
+        return None, "no ncu capture for this shape"
+    name = f"gemm_tc_kernel_{rows}x{nf[0]}x{nf[0]}_{precision}_ncu.md"
+    path = os.path.join(ROOT, "profiles", name)
+    try:
+        with open(path) as f:
+            m = re.search(r"dram_bytes_per_launch:\s*fwd=([0-9.eE+]+)\s+wgrad=([0-9.eE+]+)\s+dgrad=([0-9.eE+]+)", f.read())
+    except OSError:
+        m = None
+    if not m:
+        return None, "no ncu capture for this shape"
+    vals = [float(v) for v in m.groups()]
+    alg = (2 * rows * nf[0] + nf[0] * nf[0]) * (2 if precision == "bf16" else 4)
+    return sum(vals) / 3, (f"mean of fwd/wgrad/dgrad DRAM read+write bytes per launch from profiles/{name}; "
+                           f"operands + result of one launch: about {alg:.3g} bytes")
 
 
 def allreduce_sweep(args, rank, world, local_rank):
@@ -323,6 +357,9 @@ def main():
     ap.add_argument("--bucket-mb", type=int, default=-1,
                     help="gradient allreduce granularity in MiB (0 = per layer, -1 = library default)")
     ap.add_argument("--grad-bf16", action="store_true", help="bf16 weight gradients (configuration 5 style)")
+    ap.add_argument("--shard-update", type=int, default=-1,
+                    help="1 = reduce-scatter + SGD on the owned slice + allgather of the weights (default on 2 or "
+                         "more GPUs), 0 = allreduce + SGD on every rank")
     ap.add_argument("--p2p-bytes", type=int, default=0,
                     help="gradient sums up to this many bytes go through peer memory instead of NCCL (0 = off)")
     ap.add_argument("--trace", default=None,
@@ -354,11 +391,13 @@ def main():
     if args.impl == "reference":
         if rank != 0:
             return 0
-        ref = run_reference_cpu(args.workload, batch)
+        ref = run_reference_cpu(args.workload, batch, warmup=args.warmup, steps=args.steps)
         if ref is None:
             ref = run_port_cpu(nf, batch)
+        # steps / warmup: what was really timed (a bounded sample of the requested run)
         line = {"impl": "reference", "metric": "mlp_train_samples_per_sec", "value": ref["value"],
-                "unit": "samples/s", "n_gpus": 0, "steps": args.steps, "warmup": warmup,
+                "unit": "samples/s", "n_gpus": 0, "steps": ref["steps"], "warmup": ref["warmup"],
+                "requested": {"steps": args.steps, "warmup": args.warmup},
                 "ms_per_step": ref["ms_per_step"], "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg_common,
                 "cpu_baseline": {k: ref[k] for k in ("value", "unit", "cores", "kind", "sample")},
@@ -375,15 +414,14 @@ def main():
 
     torch.cuda.set_device(local_rank)
     dist = None
-    nccl_id = None
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-        box = [nccl_unique_id() if rank == 0 else None]
-        dist.broadcast_object_list(box, src=0)
-        nccl_id = box[0]
 
-    def e2e_id():
+    def fresh_id():
+        """An NCCL id founds one communicator: every handle of the job gets its own."""
+        if dist is None:
+            return None
         box = [nccl_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(box, src=0)
         return box[0]
@@ -394,24 +432,54 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    def max_over_ranks(v):
+    def reduce_over_ranks(v, op):
         if dist is None:
             return v
         t = torch.tensor([v], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t, op=op)
         return float(t.item())
 
-    def sum_over_ranks(v):
-        if dist is None:
-            return v
-        t = torch.tensor([v], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.SUM)
-        return float(t.item())
+    max_over_ranks = lambda v: reduce_over_ranks(v, dist.ReduceOp.MAX if dist else None)
+    sum_over_ranks = lambda v: reduce_over_ranks(v, dist.ReduceOp.SUM if dist else None)
+
+    def fail_all(what):
+        """Every rank learns of a failed check; the job ends with a non-zero exit code."""
+        if rank == 0:
+            print(json.dumps({"metric": "mlp_train_samples_per_sec", "value": None, "n_gpus": world,
+                              "error": what}))
+        sys.exit(3)
 
     prec = {"bf16": K.PREC_BF16, "tf32": K.PREC_TF32, "fp32": K.PREC_FP32}[args.precision]
-    dev = MLP(nf, batch, rank=rank, world_size=world, device=local_rank, mode=K.MODE_BASELINE, precision=prec,
-              lr=0.01, nccl_id=nccl_id, collect_timing=not args.graph, use_graph=args.graph,
-              comm_sms=args.comm_sms, grad_bf16=args.grad_bf16, ar_bucket_mb=args.bucket_mb)
+
+    # ---- the reference's start-up self-check (mlp_omp.cc:325-373, 413-416) on every rank ---------
+    # grad(s*R + i, j) = s + i + j, w = i*j, alpha = 1  ->  w = i*j - ((i + j)*N + N(N-1)/2), exact in fp32
+    kat_rows, kat_cols = 256, 512
+    ii, jj = np.meshgrid(np.arange(kat_rows), np.arange(kat_cols), indexing="ij")
+    kat = MLP([kat_cols, kat_rows], 8 * world, rank=rank, world_size=world, device=local_rank, lr=1.0,
+              nccl_id=fresh_id(), precision=prec, shard_update=args.shard_update)
+    kat.upload_weights(0, (ii * jj).astype(np.float32))
+    kat.upload_weight_grad(0, (rank + ii + jj).astype(np.float32))
+    kat.update_weight(0)
+    kat_ok = bool(np.array_equal(kat.weights(0),
+                                 (ii * jj - ((ii + jj) * world + world * (world - 1) // 2)).astype(np.float32)))
+    kat.close()
+    if sum_over_ranks(0.0 if kat_ok else 1.0) > 0:
+        fail_all("allreduce + SGD known-answer test failed")
+
+    def make(**kw):
+        opts = dict(rank=rank, world_size=world, device=local_rank, mode=K.MODE_BASELINE, precision=prec, lr=0.01,
+                    comm_sms=args.comm_sms, grad_bf16=args.grad_bf16, ar_bucket_mb=args.bucket_mb,
+                    shard_update=args.shard_update)
+        opts.update(kw)
+        if opts.get("allreduce", True):
+            opts["nccl_id"] = fresh_id()
+        m = MLP(nf, batch, **opts)
+        rng_w = np.random.default_rng(0)  # every rank draws the same weights
+        for l in range(L):
+            m.upload_weights(l, draw_weights(rng_w, winit, (nf[l + 1], nf[l])))
+        return m
+
+    dev = make(use_graph=args.graph)
     b0, b1 = dev.rows
     if args.p2p_bytes > 0 and world > 1:
         descs = [None] * world
@@ -419,93 +487,124 @@ def main():
         dev.p2p_connect(descs, args.p2p_bytes)
         dist.barrier()
 
-    # seeded synthetic data (weights seed 0, inputs seed 1, targets seed 2); every rank
-    # draws the same weights and only its own rows of the batch
-    rng_w = np.random.default_rng(0)
-    for l in range(L):
-        dev.upload_weights(l, draw_weights(rng_w, winit, (nf[l + 1], nf[l])))
+    # seeded synthetic data (weights seed 0, inputs seed 1, targets seed 2), drawn in blocks of 256
+    # rows from generators keyed by the block number: the global batch is the same whatever the
+    # number of ranks, and a rank only draws its own rows
     x_host = pinned_array((batch, nf[0]))
     t_host = pinned_array((batch, nf[-1]))
-    rng_x = np.random.default_rng([1, rank])
-    rng_t = np.random.default_rng([2, rank])
-    x_host[b0:b1] = rng_x.standard_normal((b1 - b0, nf[0]), dtype=np.float32)
-    t_host[b0:b1] = np.where(rng_t.random((b1 - b0, nf[-1])) < 0.5, -1.0, 1.0).astype(np.float32)
+    for blk in range(b0 // 256, (b1 + 255) // 256):
+        r0, r1 = blk * 256, min(batch, blk * 256 + 256)
+        xb = np.random.default_rng([1, blk]).standard_normal((r1 - r0, nf[0]), dtype=np.float32)
+        tb = np.where(np.random.default_rng([2, blk]).random((r1 - r0, nf[-1])) < 0.5, -1.0, 1.0).astype(np.float32)
+        lo, hi = max(r0, b0), min(r1, b1)
+        x_host[lo:hi] = xb[lo - r0:hi - r0]
+        t_host[lo:hi] = tb[lo - r0:hi - r0]
     dev.upload_input(x_host)
     dev.upload_target(t_host)
 
-    # ---- device-resident timing -------------------------------------------------
+    # ---- device-resident timing (no per-phase events in these steps) ----------------------------
     sampler = ClockSampler(local_rank) if rank == 0 else None  # started early: nvidia-smi needs a moment
     dev.step(warmup)
     dev.reset_timing()
     l0, tc0 = dev.launch_counts()
     barrier()
     dev.step(args.steps)
-    if args.trace and rank == 0 and not args.graph:
-        dev.write_trace(args.trace)
     barrier()
     clocks = sampler.stop() if sampler else None  # idle samples are dropped, see ClockSampler.stop
-    phase_ms, step_ms, nsteps = dev.timing()
+    _, step_ms, nsteps = dev.timing()
     l1, tc1 = dev.launch_counts()
     ms_per_step = max_over_ranks(step_ms / max(nsteps, 1))
     value = batch / (ms_per_step / 1e3)
     launches = int(sum_over_ranks(l1 - l0))
     loss = sum_over_ranks(dev.loss())
 
-    # roofline of the GEMMs on this rank (flops of the launches / their event time)
+    # ---- the replicas still hold the same weights (what the reference checks by eye on its
+    # print_checksum lines): fingerprints of every layer, equal on all ranks
+    fps = [dev.weights_fingerprint(l) for l in range(L)]
+    replicas_identical = True
+    if dist is not None:
+        box = [None] * world
+        dist.all_gather_object(box, fps)
+        replicas_identical = all(b == box[0] for b in box)
+        if not replicas_identical:
+            fail_all("the ranks' weights differ after the timed steps")
+    if not np.isfinite(loss):
+        fail_all("the loss is not finite")
+
+    # ---- per-phase breakdown: a second, short run of the same handle with an event pair around
+    # every kernel (it costs ~150 extra runtime calls per step, hence not in the timed steps above)
     bl = b1 - b0
-    gemm_flops = sum(3 * 2.0 * bl * nf[l] * nf[l + 1] for l in range(L)) * nsteps
-    # weight-gradient and input-gradient GEMMs overlap on two streams: use the time during which
-    # at least one GEMM ran, not the sum of the per-phase times
-    gemm_ms = dev.gemm_busy_ms() if not args.graph else 0.0
-    if args.graph:  # no per-phase events inside a graph: charge the whole step to the GEMMs
-        gemm_ms = step_ms
     peaks, peak_kind = measured_peaks()
-    achieved_tf = gemm_flops / (gemm_ms / 1e3) / 1e12 if gemm_ms > 0 else 0.0
-    peak_tf = peaks.get("bf16_tflops_sustained", 1400.0)
-    per_phase = {n: float(phase_ms[:, i].sum() / max(nsteps, 1)) for n, i in
-                 (("fwd_ms", K.T_FWD), ("wgrad_ms", K.T_WGT_GRAD), ("dgrad_ms", K.T_BWD),
-                  ("sgd_ms", K.T_WGT_UPDATE), ("allreduce_ms", K.T_ALLREDUCE))}
+    phase_steps = max(3, min(args.steps, 10))
+    per_phase, gemm_ms, achieved_tf = {}, 0.0, 0.0
+    gemm_flops_step = sum(3 * 2.0 * bl * nf[l] * nf[l + 1] for l in range(L))
+    if not args.graph:
+        dev.set_timing(True)
+        dev.reset_timing()
+        barrier()
+        dev.step(phase_steps)
+        if args.trace and rank == 0:
+            dev.write_trace(args.trace)
+        barrier()
+        phase_ms, timed_ms, n_ph = dev.timing()
+        gemm_ms = dev.gemm_busy_ms()
+        per_phase = {n: float(phase_ms[:, i].sum() / max(n_ph, 1)) for n, i in
+                     (("fwd_ms", K.T_FWD), ("wgrad_ms", K.T_WGT_GRAD), ("dgrad_ms", K.T_BWD),
+                      ("sgd_ms", K.T_WGT_UPDATE), ("allreduce_ms", K.T_ALLREDUCE), ("allgather_ms", K.T_ALLGATHER))}
+        per_phase["step_ms_with_events"] = timed_ms / max(n_ph, 1)
+        achieved_tf = gemm_flops_step * n_ph / (gemm_ms / 1e3) / 1e12 if gemm_ms > 0 else 0.0
+        dev.set_timing(False)
+    whole_step_tf = gemm_flops_step / (ms_per_step / 1e3) / 1e12  # every flop of the step / the whole step
+    if args.graph:
+        achieved_tf = whole_step_tf
+    peak_burst = peaks.get("bf16_tflops", 1590.0)
+    peak_sust = peaks.get("bf16_tflops_sustained", 1400.0)
     n_params = sum(nf[l] * nf[l + 1] for l in range(L))
-    sgd_bytes = n_params * (14 if args.precision == "bf16" else 12)
-    sgd_gbs = sgd_bytes / (per_phase["sgd_ms"] / 1e3) / 1e9 if per_phase["sgd_ms"] > 0 else 0.0
-    # DRAM bytes per GEMM launch (read + write) from an ncu capture of this kernel at
-    # 8192 x 4096 x 4096 bf16 (mean of two forward launches and a weight-gradient launch; the
-    # summary of that capture is kept under profiles/); other shapes were not captured
-    traffic = None
-    if args.precision == "bf16" and bl == 8192 and all(f == 4096 for f in nf):
-        traffic = (192.8e6 + 41.8e6 + 213.7e6 + 87.2e6 + 237.6e6 + 42.4e6) / 3
-    roofline = {"bound": "tensor", "kernel": "gemm_tc_kernel (fwd + wgrad + dgrad launches; flops / time with a GEMM running)",
-                "achieved": achieved_tf, "peak": peak_tf, "unit": "TFLOP/s",
-                "frac": achieved_tf / peak_tf if peak_tf else None, "traffic": traffic,
-                "traffic_note": "DRAM bytes per GEMM launch, ncu capture (algorithmic operands + result: 1.6e8)",
-                "peak_source": f"{peak_kind}: cuBLAS bf16 sustained ({peaks.get('bf16_tflops')} burst)",
-                "per_step_ms": per_phase,
-                "sgd": {"bound": "hbm", "achieved": sgd_gbs, "peak": peaks.get("hbm_gbs"), "unit": "GB/s",
-                        "frac": sgd_gbs / peaks["hbm_gbs"] if peaks.get("hbm_gbs") else None,
-                        "note": "runs on the side stream concurrently with GEMMs"}}
-    if world > 1 and per_phase["allreduce_ms"] > 0:
-        ar_bytes = n_params * (2 if args.grad_bf16 else 4)
-        busbw = ar_bytes * 2 * (world - 1) / world / (per_phase["allreduce_ms"] / 1e3) / 1e9
-        roofline["allreduce"] = {"bound": "nvlink", "busbw_gbs": busbw, "peak": 770.0, "unit": "GB/s",
-                                 "frac": busbw / 770.0,
-                                 "peak_source": "measured peer copy per direction on this pool (900 nominal)",
-                                 "note": "gradient ncclAllReduce calls timed on the side stream while GEMMs run"}
-        # How much of the allreduce hides behind compute: 1 - (t_step - t_step,no allreduce) / t_allreduce,alone
-        # (the reference's NO_ALL_REDUCE build gives the middle term, mlp_omp.cc:21). The buckets are
-        # those of the library's default rule: consecutive layers up to a quarter of all gradient bytes,
-        # each later bucket 1.5 times the one before on 4 or more GPUs.
+    traffic, traffic_note = profiled_traffic(args.precision, bl, nf)
+    roofline = {"bound": "tensor",
+                "kernel": "gemm_tc_kernel (fwd + wgrad + dgrad launches; flops / time with a GEMM running, "
+                          f"{phase_steps}-step run with per-phase events)",
+                "achieved": achieved_tf, "peak": peak_burst, "unit": "TFLOP/s",
+                "frac": achieved_tf / peak_burst if peak_burst else None,
+                "frac_of_sustained_peak": achieved_tf / peak_sust if peak_sust else None,
+                "whole_step_tflops": whole_step_tf, "whole_step_frac": whole_step_tf / peak_burst if peak_burst else None,
+                "traffic": traffic, "traffic_note": traffic_note,
+                "peak_source": f"{peak_kind}: cuBLAS bf16 burst (best of 10; the timed region lasts "
+                               f"{ms_per_step * args.steps / 1e3:.2f} s); sustained figure {peak_sust}",
+                "per_step_ms": per_phase}
+    # the SGD kernel alone on cold data (one layer's parameters; rotating sets larger than the L2)
+    big = max(nf[l] * nf[l + 1] for l in range(L))
+    sgd_ms, sgd_bytes = dev.sgd_bench(big, K.DTYPE_BF16 if args.grad_bf16 else K.DTYPE_F32,
+                                      with_bf16_copy=(args.precision == "bf16"))
+    sgd_gbs = sgd_bytes / (sgd_ms / 1e3) / 1e9
+    roofline["sgd"] = {"bound": "hbm", "isolated": {"achieved": sgd_gbs, "peak": peaks.get("hbm_gbs"), "unit": "GB/s",
+                                                    "frac": sgd_gbs / peaks["hbm_gbs"] if peaks.get("hbm_gbs") else None,
+                                                    "bytes_per_launch": sgd_bytes, "ms_per_launch": sgd_ms,
+                                                    "note": "sgd_kernel alone, CUDA events, operands not in L2"},
+                       "in_step_ms": per_phase.get("sgd_ms"),
+                       "note": "in the step it runs on the update stream next to the GEMMs"}
+
+    if world > 1 and not args.graph:
+        # The collectives alone (same sizes as the step's buckets), the step without any collective
+        # (the reference's NO_ALL_REDUCE build, mlp_omp.cc:21), and from the three:
+        # hidden fraction = 1 - (t_step - t_step,no collectives) / t_collectives,alone
         es = 2 if args.grad_bf16 else 4
+        ws = 2 if args.precision == "bf16" else 4  # bytes per weight the allgather carries
+        shard = args.shard_update != 0
         buckets = gradient_buckets([nf[l] * nf[l + 1] * es for l in range(L)], world, args.bucket_mb)
-        t_alone = 0.0
+        t_alone, wire = 0.0, 0.0
         for b in buckets:
+            cnt = (b // es + 128 * world - 1) // (128 * world) * (128 * world)
             barrier()
-            ms, _ = dev.allreduce_bench(b // es, K.DTYPE_BF16 if args.grad_bf16 else K.DTYPE_F32, 3, 10)
-            t_alone += max_over_ranks(ms)
-        noar = MLP(nf, batch, rank=rank, world_size=world, device=local_rank, mode=K.MODE_BASELINE, precision=prec,
-                   lr=0.01, allreduce=False, grad_bf16=args.grad_bf16)
-        rng_n = np.random.default_rng(0)
-        for l in range(L):
-            noar.upload_weights(l, draw_weights(rng_n, winit, (nf[l + 1], nf[l])))
+            if shard:
+                t_alone += max_over_ranks(dev.collective_bench(1, cnt, K.DTYPE_BF16 if args.grad_bf16 else K.DTYPE_F32))
+                barrier()
+                t_alone += max_over_ranks(dev.collective_bench(2, cnt, K.DTYPE_BF16 if ws == 2 else K.DTYPE_F32))
+                wire += cnt * (es + ws) * (world - 1) / world
+            else:
+                t_alone += max_over_ranks(dev.collective_bench(0, cnt, K.DTYPE_BF16 if args.grad_bf16 else K.DTYPE_F32))
+                wire += cnt * es * 2 * (world - 1) / world
+        noar = make(allreduce=False)
         noar.upload_input(x_host)
         noar.upload_target(t_host)
         noar.step(warmup)
@@ -516,11 +615,17 @@ def main():
         _, ms_noar, n_noar = noar.timing()
         noar.close()
         t_noar = max_over_ranks(ms_noar / max(n_noar, 1))
-        roofline["allreduce"].update({
-            "alone_ms_per_step": t_alone, "buckets_bytes": buckets, "step_ms_without_allreduce": t_noar,
-            "hidden_fraction": 1.0 - (ms_per_step - t_noar) / t_alone if t_alone > 0 else None,
-            "busbw_alone_gbs": sum(buckets) * 2 * (world - 1) / world / (t_alone / 1e3) / 1e9 if t_alone > 0 else None,
-            "frac_alone": sum(buckets) * 2 * (world - 1) / world / (t_alone / 1e3) / 1e9 / 770.0 if t_alone > 0 else None})
+        in_step = per_phase.get("allreduce_ms", 0.0) + per_phase.get("allgather_ms", 0.0)
+        nvlink = 900.0
+        roofline["allreduce"] = {
+            "bound": "nvlink", "route": "reduce-scatter + owned-slice SGD + allgather" if shard else "allreduce",
+            "wire_bytes_per_gpu_per_step": wire, "buckets_bytes": buckets,
+            "alone_ms_per_step": t_alone, "busbw_alone_gbs": wire / (t_alone / 1e3) / 1e9 if t_alone > 0 else None,
+            "in_step_ms": in_step, "busbw_in_step_gbs": wire / (in_step / 1e3) / 1e9 if in_step > 0 else None,
+            "peak": nvlink, "unit": "GB/s", "frac_alone": wire / (t_alone / 1e3) / 1e9 / nvlink if t_alone > 0 else None,
+            "peak_source": "nominal NVLink 5 bandwidth per direction per GPU",
+            "step_ms_without_allreduce": t_noar,
+            "hidden_fraction": 1.0 - (ms_per_step - t_noar) / t_alone if t_alone > 0 else None}
 
     # ---- end to end through the host-facing call --------------------------------
     # Every step: this step's inputs and targets are copied from pinned host memory
@@ -529,12 +634,7 @@ def main():
     e2e = None
     if not args.no_e2e:
         dev.close()
-        dev = MLP(nf, batch, rank=rank, world_size=world, device=local_rank, mode=K.MODE_BASELINE,
-                  precision=prec, lr=0.01, nccl_id=None if world == 1 else e2e_id(), collect_timing=False,
-                  comm_sms=args.comm_sms, grad_bf16=args.grad_bf16, ar_bucket_mb=args.bucket_mb)
-        rng_w = np.random.default_rng(0)
-        for l in range(L):
-            dev.upload_weights(l, draw_weights(rng_w, winit, (nf[l + 1], nf[l])))
+        dev = make()
         xp = x_host.ctypes.data_as(K._fp)
         tp = t_host.ctypes.data_as(K._fp)
 
@@ -569,6 +669,8 @@ def main():
                 "scaling": "strong", "vs_baseline": None, "dtype": args.precision, "data": "synthetic",
                 "config": cfg_common, "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
                 "gpu_launches": launches, "clocks": clocks, "loss": loss,
+                "kat": "pass", "replicas_identical": replicas_identical,
+                "weights_fingerprint": [f"{v:016x}" for v in fps[:4]],
                 "gemm_tflops_per_gpu": achieved_tf}
         print(json.dumps(line))
     if dist is not None:

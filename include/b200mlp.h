@@ -90,6 +90,14 @@ typedef struct {
                                far better) and, with 4 or more GPUs, each later one 1.5 times the
                                bytes of the one before (the sums then limit the step, so the first
                                should start early and the rest be few) */
+  int shard_update;         /* how the summed gradient reaches the weights on 2 or more GPUs:
+                               1 = like the reference (mlp_omp.cc:90-146, 240-258): reduce-scatter of each
+                               gradient bucket, SGD on the 1/world slice of the weights this rank owns,
+                               allgather of the updated weights (of their bf16 operand copy in BF16
+                               precision: 25 % fewer bytes on the wire, and only the owner keeps that
+                               slice's fp32 master weights current until b2_download_weights or
+                               b2_allreduce_sgd gathers them, which makes those two calls collective);
+                               0 = allreduce, then every rank updates all weights; -1 = default: 1 */
   float lr;                 /* SGD step (the reference hard-codes 1e-10, mlp_omp.cc:609) */
   const void* nccl_unique_id; /* B2_NCCL_ID_BYTES bytes from b2_nccl_unique_id(), shared by all
                                  ranks; NULL when world_size == 1 */
@@ -100,7 +108,9 @@ typedef struct {
 /* Phases of the step, in the order of the reference's Breakdown enum
  * (mlp_bench_common.h:12-20). */
 enum { B2_T_FWD = 0, B2_T_WGT_GRAD = 1, B2_T_BWD = 2, B2_T_WGT_UPDATE = 3,
-       B2_T_ALLREDUCE = 4, B2_T_NUM = 5 };
+       B2_T_ALLREDUCE = 4, /* gradient allreduce, or reduce-scatter with shard_update (WGT_UPDATE_REDUCE_SCATTER) */
+       B2_T_ALLGATHER = 5, /* allgather of the updated weights with shard_update (WGT_UPDATE_ALLGATHER) */
+       B2_T_NUM = 6 };
 
 /* Defaults: mode BASELINE, precision FP32, world 1, allreduce/overlap/input_grad on, comm_sms -1. */
 int b2_config_default(b2_config* cfg);
@@ -125,7 +135,10 @@ const char* b2_last_error(const b2_handle* h);
 /* Rows [begin,end) of the global batch this handle owns (Partition.cc:34-51). */
 int b2_batch_range(const b2_handle* h, int* begin, int* end);
 
-/* init_matrices (mlp_bench_common.cc:16-33): weights[l] replica rows, F_{l+1} x F_l. */
+/* init_matrices (mlp_bench_common.cc:16-33): weights[l] replica rows, F_{l+1} x F_l.
+ * With shard_update in BF16 precision b2_download_weights is collective after steps have run:
+ * every rank has to call it (for the same layers in the same order), because each rank holds
+ * current fp32 master weights only for the slices it owns and the call gathers them first. */
 int b2_upload_weights(b2_handle* h, int layer, const float* host, size_t ld);
 int b2_download_weights(b2_handle* h, int layer, float* host, size_t ld);
 /* activations[0] (mlp_bench_common.cc:18) and the +-1 targets of BASELINE mode.
@@ -211,8 +224,16 @@ const char* b2_noalloc_last_error(void);
 
 /* update_weight (mlp_omp.cc:297-323) on layer `l`: sum weight_grads[l] over all
  * ranks, then w = fma(-lr, sum, w). The reference's known-answer test
- * (mlp_omp.cc:325-373) runs through this call. */
+ * (mlp_omp.cc:325-373) runs through this call. With shard_update it takes the reference's
+ * own route: reduce-scatter, SGD on the owned slice, allgather of the weights. */
 int b2_allreduce_sgd(b2_handle* h, int layer);
+
+/* In-place sum over all ranks of `count` elements of `dtype` (b2_dtype) at the DEVICE pointer
+ * `dev_buf` of this handle's GPU, through the handle's communicator on its main stream;
+ * returns after the result is there. The gradient-allreduce sweep on caller-owned buffers
+ * (the reference sums caller-owned Matrix buffers, update_weight(Matrix*, ...), mlp_omp.cc:297);
+ * with one rank the buffer is left as it is. */
+int b2_allreduce(b2_handle* h, void* dev_buf, size_t count, int dtype);
 
 /* Gradient-allreduce sweep: sums `count` elements of `dtype` filled with
  * U(-1,1) from seed = rank across all ranks, `iters` timed repetitions after
@@ -220,6 +241,40 @@ int b2_allreduce_sgd(b2_handle* h, int layer);
  * checksum (optional) the sum of the first min(count,4096) result elements. */
 int b2_allreduce_bench(b2_handle* h, size_t count, int dtype, int warmup, int iters,
                        double* ms_per_iter, double* checksum);
+/* The same sweep for each of the three collectives of the step: kind 0 = allreduce, 1 =
+ * reduce-scatter (mlp_omp.cc:56-169: each rank ends with the sum of its 1/world slice), 2 =
+ * allgather (mlp_omp.cc:171-295 after its SGD: each rank's slice to all); `count` is the whole
+ * buffer in elements and must divide by the number of ranks for kinds 1 and 2. */
+int b2_collective_bench(b2_handle* h, int kind, size_t count, int dtype, int warmup, int iters,
+                        double* ms_per_iter, double* checksum);
+
+/* The SGD kernel alone on `nparams` parameters (w = fma(-lr, g, w), gradients of grad_dtype,
+ * optionally also writing the bf16 operand copy), on parameter sets used in rotation that
+ * together exceed the L2 several times: *ms_per_iter = device time of one launch,
+ * *bytes_per_iter = the algorithmic bytes it moves (read w, read g, write w, write copy). */
+int b2_sgd_bench(b2_handle* h, size_t nparams, int grad_dtype, int with_bf16_copy, int warmup, int iters,
+                 double* ms_per_iter, double* bytes_per_iter);
+
+/* Switches the per-phase event timing of b2_step (b2_config.collect_timing) on or off. */
+int b2_set_timing(b2_handle* h, int collect_timing);
+
+/* Order-independent fingerprint (sum of the 32-bit words modulo 2^64) of layer l's weights as
+ * the next forward pass reads them (the bf16 operand copy in BF16 precision, the fp32 weights
+ * otherwise): equal on every rank of a data-parallel job exactly when the replicas hold the
+ * same bits. The device counterpart of comparing print_checksum lines by eye
+ * (mlp_bench_common.cc:152-168). */
+int b2_weights_fingerprint(b2_handle* h, int layer, unsigned long long* fingerprint);
+
+/* One GEMM of the step alone, for roofline measurements per call form and shape: form 0 = forward
+ * (mlp_omp.cc:474-488: A m x k, B n x k), 1 = weight gradient (:565-580: A stored k x m, B stored
+ * k x n), 2 = input gradient (:655-671: A m x k, B k x n); `precision`, `epilogue` and the output
+ * type as in the step (out_dtype a b2_dtype; bf16 output needs BF16 precision); sms = number of SMs
+ * the persistent tensor-core grid may use (0 = all). Operands are seeded U(-1,1) device buffers,
+ * as many sets as it takes to exceed the L2 several times over, used in rotation so that every
+ * launch reads its operands from HBM like the launches of a step do. *ms_per_iter = device time
+ * of one launch (CUDA events around `iters` back-to-back launches after `warmup`). */
+int b2_gemm_bench(b2_handle* h, int form, int m, int n, int k, int precision, int epilogue, int out_dtype,
+                  int sms, int warmup, int iters, double* ms_per_iter);
 
 /* Peer-memory path for small gradient messages (the 1 MiB layers of the deep narrow
  * configuration, where a library collective is latency-bound). The reference moves its
@@ -232,15 +287,28 @@ int b2_allreduce_bench(b2_handle* h, size_t count, int dtype, int warmup, int it
  *   3. every rank: b2_p2p_connect(h, all_descs, max_bytes) with all_descs in rank order
  * From then on gradient sums of at most max_bytes (fp32 gradients, no graph replay) bypass
  * NCCL; larger ones still use it. All ranks must pass the same max_bytes, and none may destroy
- * its handle while another still runs steps. A rank that waits longer than a second for
- * another gets B2_ERR_TIMEOUT from its next synchronising call and falls back to NCCL-only. */
+ * its handle while another still runs steps. A rank that waits longer than the wait limit (one
+ * second unless b2_p2p_set_wait_ms changed it; the reference spins without a limit,
+ * mlp_omp.cc:120-121,267-268) for another gets B2_ERR_TIMEOUT from its next synchronising call
+ * (b2_step, b2_sync, b2_allreduce_sgd, b2_wait_loss) and falls back to NCCL-only; the peer
+ * launches still queued behind the one that gave up return at once. */
 #define B2_P2P_DESC_BYTES 128
 int b2_p2p_describe(b2_handle* h, void* desc);
 int b2_p2p_connect(b2_handle* h, const void* descs, size_t max_bytes);
+/* How long one flag wait of the peer-memory path may last, 1 .. 60000 ms (default 1000). Ranks
+ * that reach a gradient sum further apart than this (first-call module loads, a slow host
+ * thread) time out, so embedders with loosely coupled ranks raise it. */
+int b2_p2p_set_wait_ms(b2_handle* h, int ms);
 /* The same kernel with all `world` ranks emulated on ONE GPU (one cooperative launch; for
  * machines with fewer GPUs than ranks): bufs[r] = rank r's `count` host floats, replaced by the
  * sum over ranks. No handle needed. The reference has no counterpart. */
 int b2_p2p_emulate(int device, int world, float* const* bufs, size_t count);
+/* Same with a chosen wait limit and, when lagging_rank >= 0, with that rank one call behind
+ * the others, so that every wait on it runs out: the call then returns B2_ERR_TIMEOUT after
+ * about two wait limits and leaves bufs untouched (how a lost rank looks to the others, made
+ * on the host side without any fault on the device). lagging_rank = -1: no rank lags. */
+int b2_p2p_emulate_opts(int device, int world, float* const* bufs, size_t count, int wait_ms,
+                        int lagging_rank);
 
 /* Device times in milliseconds accumulated since the last reset:
  * phase_ms[l * B2_T_NUM + phase] per layer (needs collect_timing), and

@@ -88,9 +88,34 @@ static void sgemm_loops(int transa, int transb, int m, int n, int k, float alpha
   free(bt);
 }
 
+/* Re-association switch: with g_ksplit = s > 1 every GEMM is computed as s partial
+ * products over consecutive ranges of the contraction index that are added up one
+ * after the other - the same sum in another floating-point order. Two oracles that
+ * differ only in this switch measure how sensitive a configuration is to the order of
+ * fp32 additions (the noise floor any two correct implementations are apart). */
+static int g_ksplit = 1;
+void orc_set_ksplit(int s) { g_ksplit = s < 1 ? 1 : s; }
+
+static void sgemm_one(int transa, int transb, int m, int n, int k, float alpha, const float* a,
+                      int lda, const float* b, int ldb, float beta, float* c, int ldc);
+
 void orc_sgemm(int transa, int transb, int m, int n, int k, float alpha, const float* a,
                int lda, const float* b, int ldb, float beta, float* c, int ldc) {
   if (m <= 0 || n <= 0) return;
+  if (g_ksplit <= 1 || k < 2 * g_ksplit) {
+    sgemm_one(transa, transb, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc);
+    return;
+  }
+  for (int s = 0; s < g_ksplit; ++s) {
+    const int k0 = (int)((long long)k * s / g_ksplit), k1 = (int)((long long)k * (s + 1) / g_ksplit);
+    const float* as = transa ? a + (size_t)k0 * lda : a + k0;
+    const float* bs = transb ? b + k0 : b + (size_t)k0 * ldb;
+    sgemm_one(transa, transb, m, n, k1 - k0, alpha, as, lda, bs, ldb, s == 0 ? beta : 1.f, c, ldc);
+  }
+}
+
+static void sgemm_one(int transa, int transb, int m, int n, int k, float alpha, const float* a,
+                      int lda, const float* b, int ldb, float beta, float* c, int ldc) {
   if (g_sgemm) {
     /* CblasRowMajor = 101, CblasNoTrans = 111, CblasTrans = 112 */
     g_sgemm(101, transa ? 112 : 111, transb ? 112 : 111, m, n, k, alpha, a, lda, b, ldb,

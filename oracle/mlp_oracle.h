@@ -53,6 +53,10 @@ typedef void (*orc_sgemm_fn)(int order, int transa, int transb, int m, int n, in
 /* Route the oracle's GEMMs through an external BLAS (NULL = built-in loops). */
 void orc_set_sgemm(orc_sgemm_fn fn);
 
+/* s > 1: every GEMM is summed as s partial products over consecutive ranges of the
+ * contraction index (same mathematics, another fp32 addition order); 1 = off. */
+void orc_set_ksplit(int s);
+
 /* Row-major C = alpha*op(A)*op(B) + beta*C with cblas argument meaning. */
 void orc_sgemm(int transa, int transb, int m, int n, int k, float alpha,
                const float* a, int lda, const float* b, int ldb, float beta,

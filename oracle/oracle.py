@@ -40,7 +40,6 @@ def _f32(a):
 def find_openblas():
     env = os.environ.get("B2_OPENBLAS_PATH")
     pats = [env] if env else []
-    pats += ["/opt/*/.venv/lib/python3*/site-packages/scipy.libs/libscipy_openblas-*.so"]
     try:
         import scipy
         pats.append(os.path.join(os.path.dirname(os.path.dirname(scipy.__file__)), "scipy.libs",
@@ -82,6 +81,7 @@ def lib():
         L.orc_sgemm.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, _fp, C.c_int,
                                 _fp, C.c_int, C.c_float, _fp, C.c_int]
         L.orc_set_sgemm.argtypes = [C.c_void_p]
+        L.orc_set_ksplit.argtypes = [C.c_int]
         L.orc_batch_range.argtypes = [C.c_int, C.c_int, C.c_int, _ip, _ip]
         L.orc_kat_fill.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, _fp, _fp, C.c_size_t]
         L.orc_kat_expected.argtypes = [C.c_int, C.c_int, C.c_int, _fp, C.c_size_t]
@@ -116,6 +116,13 @@ def use_openblas(threads=None):
 
 def use_builtin_gemm():
     lib().orc_set_sgemm(None)
+
+
+def set_ksplit(s):
+    """s > 1: the oracle sums every GEMM as s partial products over consecutive ranges of the
+    contraction index - the same sum in another fp32 order. Comparing two oracle runs that
+    differ only in this switch gives the configuration's own sensitivity to summation order."""
+    lib().orc_set_ksplit(int(s))
 
 
 def sgemm(transa, transb, a, b, alpha=1.0):

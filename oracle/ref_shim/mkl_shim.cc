@@ -37,8 +37,6 @@ void bind_blas() {
 #ifdef B2_OPENBLAS_DEFAULT
   if (!h) h = try_open(B2_OPENBLAS_DEFAULT);
 #endif
-  if (!h) h = try_open("/opt/*/.venv/lib/python3*/site-packages/scipy.libs/libscipy_openblas-*.so");
-  if (!h) h = try_open("/usr/lib/python3*/site-packages/scipy.libs/libscipy_openblas-*.so");
   if (h) {
     g_sgemm = (sgemm_t)dlsym(h, "scipy_cblas_sgemm");
     using setn_t = void (*)(int);

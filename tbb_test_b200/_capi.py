@@ -15,7 +15,7 @@ MODE_REF, MODE_BASELINE = 0, 1
 PREC_FP32, PREC_TF32, PREC_BF16 = 0, 1, 2
 DTYPE_F32, DTYPE_BF16 = 0, 1
 EPI_NONE, EPI_RELU, EPI_MASK = 0, 1, 2
-T_FWD, T_WGT_GRAD, T_BWD, T_WGT_UPDATE, T_ALLREDUCE, T_NUM = 0, 1, 2, 3, 4, 5
+T_FWD, T_WGT_GRAD, T_BWD, T_WGT_UPDATE, T_ALLREDUCE, T_ALLGATHER, T_NUM = 0, 1, 2, 3, 4, 5, 6
 NCCL_ID_BYTES = 128
 P2P_DESC_BYTES = 128
 NOALLOC_MAX_OPERAND_ELEMS = 4 * 1024 * 1024
@@ -29,7 +29,7 @@ class Config(C.Structure):
         ("nlayers", C.c_int), ("nfeatures", C.POINTER(C.c_int)), ("batch", C.c_int), ("rank", C.c_int),
         ("world_size", C.c_int), ("device", C.c_int), ("mode", C.c_int), ("precision", C.c_int),
         ("grad_bf16", C.c_int), ("allreduce", C.c_int), ("overlap", C.c_int), ("input_grad", C.c_int),
-        ("collect_timing", C.c_int), ("use_graph", C.c_int), ("force_simt", C.c_int), ("comm_sms", C.c_int), ("ar_bucket_mb", C.c_int), ("lr", C.c_float),
+        ("collect_timing", C.c_int), ("use_graph", C.c_int), ("force_simt", C.c_int), ("comm_sms", C.c_int), ("ar_bucket_mb", C.c_int), ("shard_update", C.c_int), ("lr", C.c_float),
         ("nccl_unique_id", C.c_void_p),
     ]
 
@@ -70,10 +70,19 @@ SYMBOLS = {
                                        C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p]),
     "b2_noalloc_last_error": (C.c_char_p, []),
     "b2_allreduce_sgd": (C.c_int, [_H, C.c_int]),
+    "b2_allreduce": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_int]),
     "b2_allreduce_bench": (C.c_int, [_H, C.c_size_t, C.c_int, C.c_int, C.c_int, _dp, _dp]),
+    "b2_collective_bench": (C.c_int, [_H, C.c_int, C.c_size_t, C.c_int, C.c_int, C.c_int, _dp, _dp]),
+    "b2_sgd_bench": (C.c_int, [_H, C.c_size_t, C.c_int, C.c_int, C.c_int, C.c_int, _dp, _dp]),
+    "b2_set_timing": (C.c_int, [_H, C.c_int]),
+    "b2_weights_fingerprint": (C.c_int, [_H, C.c_int, C.POINTER(C.c_ulonglong)]),
+    "b2_gemm_bench": (C.c_int, [_H, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                C.c_int, _dp]),
     "b2_p2p_describe": (C.c_int, [_H, C.c_void_p]),
     "b2_p2p_connect": (C.c_int, [_H, C.c_void_p, C.c_size_t]),
     "b2_p2p_emulate": (C.c_int, [C.c_int, C.c_int, C.POINTER(_fp), C.c_size_t]),
+    "b2_p2p_emulate_opts": (C.c_int, [C.c_int, C.c_int, C.POINTER(_fp), C.c_size_t, C.c_int, C.c_int]),
+    "b2_p2p_set_wait_ms": (C.c_int, [_H, C.c_int]),
     "b2_get_timing": (C.c_int, [_H, _dp, _dp, C.POINTER(C.c_longlong)]),
     "b2_get_gemm_busy_ms": (C.c_int, [_H, _dp]),
     "b2_reset_timing": (C.c_int, [_H]),
@@ -93,6 +102,16 @@ def lib():
             raise ImportError(
                 f"{path} is missing: build it with `python -m tbb_test_b200.build` "
                 "(there is no CPU or PyTorch fallback)")
+        if "B2_NCCL_PATH" not in os.environ:
+            # prefer the NCCL wheel of this interpreter (the one PyTorch itself loads) over a
+            # system copy; the library falls back to the loader's search path without it
+            import importlib.util
+            spec = importlib.util.find_spec("nvidia")
+            for base in (spec.submodule_search_locations if spec else []):
+                cand = os.path.join(base, "nccl", "lib", "libnccl.so.2")
+                if os.path.exists(cand):
+                    os.environ["B2_NCCL_PATH"] = cand
+                    break
         L = C.CDLL(path, mode=C.RTLD_GLOBAL)
         for name, (res, args) in SYMBOLS.items():
             if path != LIB_PATH and not hasattr(L, name):

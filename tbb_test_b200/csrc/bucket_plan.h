@@ -45,4 +45,33 @@ inline void plan_gradient_buckets(const size_t* layer_bytes, int nlayers, int wo
   }
 }
 
+// Layout of the gradient slab and of the weight slabs that mirror it: layers in the order
+// backward produces their gradients (L-1 first), each padded to a multiple of 128 * world_size
+// elements, so that every layer starts on a 256-byte boundary in a bf16 slab and every bucket
+// of consecutive layers divides evenly among the ranks. Returns the slab's element count.
+inline size_t plan_slab_layout(const size_t* layer_elems, int nlayers, int world_size, size_t* offset,
+                               size_t* padded) {
+  const size_t align = (size_t)128 * (size_t)(world_size < 1 ? 1 : world_size);
+  size_t total = 0;
+  for (int l = nlayers - 1; l >= 0; --l) {
+    offset[l] = total;
+    padded[l] = (layer_elems[l] + align - 1) / align * align;
+    total += padded[l];
+  }
+  return total;
+}
+
+// Element range [begin, begin + count) of the bucket of layers [low, high] in the slabs, and
+// the slice of it `rank` owns under the sharded update (the reduce-scatter leaves the sum of
+// that slice with the rank, the rank updates those weights and the allgather distributes
+// them): the reference's chunk ownership (mlp_omp.cc:80-94, 228) per bucket instead of per layer.
+inline void plan_bucket_slice(const size_t* offset, const size_t* padded, int low, int high, int world_size, int rank,
+                              size_t* begin, size_t* count, size_t* slice_begin, size_t* slice_count) {
+  *begin = offset[high];
+  *count = offset[low] + padded[low] - offset[high];
+  const size_t per = *count / (size_t)world_size;
+  if (slice_begin) *slice_begin = *begin + (size_t)rank * per;
+  if (slice_count) *slice_count = per;
+}
+
 }  // namespace b2

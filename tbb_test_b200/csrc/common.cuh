@@ -52,6 +52,10 @@ cudaError_t gemm_simt_launch(const GemmDesc& g, cudaStream_t stream);
 struct TcPlan;  // opaque: tensor maps + tile choice for one GEMM site
 TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t errlen);
 void gemm_tc_plan_destroy(TcPlan* p);
+// ReLU bit plane of a plan (one bit per element of C, words of 32 columns, ld_words words per
+// row): mask_out on a forward plan with the ReLU epilogue, mask_in on an input-gradient plan with
+// the mask epilogue (read instead of the activation). False when the plan cannot use one.
+bool gemm_tc_plan_set_mask(TcPlan* plan, uint32_t* mask_out, const uint32_t* mask_in, long long ld_words);
 cudaError_t gemm_tc_launch(const TcPlan* p, cudaStream_t stream, unsigned int* status);
 
 // Small-message allreduce over peer memory (p2p_allreduce.cu). Every rank's gradient slab and
@@ -72,6 +76,7 @@ struct P2pParams {
   unsigned int epoch;         // call counter, > 0, the same on every rank for the same call
   unsigned int* ctas_done;    // this rank's own counter, zero between calls
   unsigned int* status;       // this rank's own word, set non-zero when a wait gave up
+  unsigned long long wait_ns; // how long a flag wait may last before the rank gives up
 };
 // One rank's launch (every rank launches its own, each on its own GPU).
 cudaError_t p2p_allreduce_launch(const P2pParams& p, int cta_limit, cudaStream_t stream);
@@ -88,6 +93,8 @@ cudaError_t loss_grad_launch(const float* y, const float* target, void* dz, int 
 // w = fma(-lr, g, w); optional bf16 copy of the new weights
 cudaError_t sgd_launch(float* w, const void* g, int g_type, __nv_bfloat16* w_bf16, size_t n, float lr,
                        int sm_count, cudaStream_t s);
+// *out += sum of the 32-bit words of buf modulo 2^64 (out must be zeroed by the caller)
+cudaError_t fingerprint_launch(const void* buf, size_t bytes, unsigned long long* out, cudaStream_t s);
 cudaError_t fill_uniform_launch(void* buf, int type, size_t n, uint64_t seed, float lo, float hi,
                                 cudaStream_t s);
 

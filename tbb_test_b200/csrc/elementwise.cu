@@ -155,6 +155,23 @@ __global__ void __launch_bounds__(256) fill_uniform_kernel(T* __restrict__ buf, 
   }
 }
 
+// Order-independent fingerprint of a buffer: the sum of its 32-bit words modulo 2^64
+// (exact whatever the order of additions, unlike a floating-point checksum).
+__global__ void __launch_bounds__(256) fingerprint_kernel(const uint32_t* __restrict__ words, size_t n,
+                                                          unsigned long long* __restrict__ out) {
+  unsigned long long local = 0;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) local += words[i];
+  __shared__ unsigned long long red[256];
+  red[threadIdx.x] = local;
+  __syncthreads();
+  for (int s = 128; s > 0; s >>= 1) {
+    if (threadIdx.x < s) red[threadIdx.x] += red[threadIdx.x + s];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) atomicAdd(out, red[0]);
+}
+
 int grid_for(size_t work_items, int sm_count, int per_sm) {
   size_t blocks = (work_items + 255) / 256;
   size_t cap = (size_t)sm_count * per_sm;
@@ -215,6 +232,13 @@ cudaError_t convert_f32_to_bf16(const float* src, __nv_bfloat16* dst, size_t n, 
 cudaError_t convert_bf16_to_f32(const __nv_bfloat16* src, float* dst, size_t n, cudaStream_t s) {
   if (n == 0) return cudaSuccess;
   bf16_to_f32_kernel<<<grid_for(n, device_sms(), 8), 256, 0, s>>>(src, dst, n);
+  return cudaGetLastError();
+}
+
+cudaError_t fingerprint_launch(const void* buf, size_t bytes, unsigned long long* out, cudaStream_t s) {
+  const size_t n = bytes / 4;  // whole 32-bit words (the buffers fingerprinted here are multiples of 4 bytes)
+  if (n == 0) return cudaSuccess;
+  fingerprint_kernel<<<grid_for(n, device_sms(), 8), 256, 0, s>>>(static_cast<const uint32_t*>(buf), n, out);
   return cudaGetLastError();
 }
 

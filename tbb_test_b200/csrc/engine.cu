@@ -59,9 +59,23 @@ struct b2_handle {
   std::vector<cudaEvent_t> ev_ar;  // per layer that closes a bucket: its allreduce is done
   cudaEvent_t ev_dz_last = nullptr;
   bool wg_stream = false;
-  std::vector<float*> w;
-  std::vector<__nv_bfloat16*> w16;
+  // Weights live in slabs laid out like the gradient slab (same element offsets), so that a
+  // bucket of consecutive layers is one contiguous range in all three: the reduce-scatter of
+  // the gradients, the SGD of the owned slice and the allgather of the weights each take one call.
+  float* w_slab = nullptr;
+  __nv_bfloat16* w16_slab = nullptr;
+  std::vector<float*> w;             // w_slab + dw_off[l]
+  std::vector<__nv_bfloat16*> w16;   // w16_slab + dw_off[l]
+  bool shard = false;          // reduce-scatter + owned-slice SGD + allgather instead of allreduce + full SGD
+  bool masters_stale = false;  // BF16 precision with shard: ranks hold current fp32 masters only for their slices
+  std::vector<size_t> dw_pad;  // padded element count of layer l in the slabs (multiple of 128 * world)
+  std::vector<char> bucket_full;  // for the layer closing a bucket: 1 = this bucket is summed in full on every rank
+  std::vector<cudaEvent_t> ev_shard;  // per bucket-closing layer: owned-slice SGD done
   std::vector<void*> dw, act, dz;
+  // ReLU bit planes (BASELINE mode, tensor-core kernels): relu_bits[l] holds one bit per element
+  // of act[l], l = 1 .. L-1, written by the forward epilogue of layer l-1 and read by the
+  // input-gradient epilogue of layer l in place of the activation (1/16 of its bytes)
+  std::vector<uint32_t*> relu_bits;
   // All weight gradients live in one slab, last layer first (the order backward produces
   // them), so that consecutive layers can be summed by one collective call ("bucket").
   void* dw_slab = nullptr;
@@ -71,6 +85,7 @@ struct b2_handle {
   bool p2p_ready = false;
   size_t p2p_max_bytes = 0;
   unsigned int p2p_epoch = 0;
+  unsigned long long p2p_wait_ns = 1000000000ull;  // b2_p2p_set_wait_ms
   unsigned int* p2p_ctas_done = nullptr;
   float* p2p_slab[P2P_MAX_RANKS] = {};
   unsigned int* p2p_flags[P2P_MAX_RANKS] = {};
@@ -85,6 +100,7 @@ struct b2_handle {
   size_t stage_elems = 0;
   double* loss_dev = nullptr;  // [2]: one accumulator per input slot
   unsigned int* status_dev = nullptr;
+  unsigned long long* fp_dev = nullptr;  // accumulator of b2_weights_fingerprint
   float* tc_ws = nullptr;           // stream-K workspace shared by this handle's GEMMs (they
   unsigned int* tc_ws_flags = nullptr;  // all run on the main stream, one after the other)
   std::vector<cudaEvent_t> ev_wgrad, ev_dgrad, ev_upd;
@@ -187,6 +203,8 @@ cudaEvent_t phase_ev(b2_handle* h, int l, int phase, int end) {
   return h->ev_phase[(((size_t)h->ev_iter * h->L + l) * B2_T_NUM + phase) * 2 + end];
 }
 
+int check_comm(b2_handle* h);
+
 int check_status(b2_handle* h) {
   unsigned int st = 0;
   CK(h, cudaMemcpy(&st, h->status_dev, sizeof st, cudaMemcpyDeviceToHost));
@@ -200,6 +218,22 @@ int check_status(b2_handle* h) {
                   "the peer path is switched off for this handle", st);
     }
     return fail(h, B2_ERR_TIMEOUT, "tensor-core GEMM gave up waiting on a pipeline barrier (role %u)", st);
+  }
+  return check_comm(h);
+}
+
+// Asynchronous errors of the communicator (a peer process that died, a network fault): reported
+// as B2_ERR_NCCL, and the communicator is aborted so that no later call blocks on it.
+int check_comm(b2_handle* h) {
+  if (!h->comm || !nccl_api().CommGetAsyncError) return B2_OK;
+  int async = ncclSuccess;
+  if (nccl_api().CommGetAsyncError(h->comm, &async) != ncclSuccess) return B2_OK;
+  if (async != ncclSuccess && async != ncclInProgress) {
+    const char* what = nccl_api().GetErrorString(async);
+    if (nccl_api().CommAbort) nccl_api().CommAbort(h->comm);
+    h->comm = nullptr;
+    return fail(h, B2_ERR_NCCL, "the communicator reported an asynchronous error (%s) and was aborted; "
+                "destroy the handles of this job", what ? what : "?");
   }
   return B2_OK;
 }
@@ -308,6 +342,19 @@ int build_sites(b2_handle* h) {
       make_site(h, h->wgrad0_alt, tc, wg_sms);
     }
   }
+  // ReLU bit planes: used for a layer only if both its producer (forward of the layer below) and
+  // its consumer (input gradient of the layer itself) run on the tensor-core kernel
+  for (int l = 1; l < L; ++l) {
+    if (!h->relu_bits[l] || !h->fwd[l - 1].plan || !h->dgrad[l].plan) continue;
+    const long long ldw = h->nf[l] / 32;
+    if (l == 1 && !h->fwd0_alt.plan) continue;
+    if (!gemm_tc_plan_set_mask(h->fwd[l - 1].plan, h->relu_bits[l], nullptr, ldw)) continue;
+    if (!gemm_tc_plan_set_mask(h->dgrad[l].plan, nullptr, h->relu_bits[l], ldw)) {
+      gemm_tc_plan_set_mask(h->fwd[l - 1].plan, nullptr, nullptr, ldw);
+      continue;
+    }
+    if (l == 1) gemm_tc_plan_set_mask(h->fwd0_alt.plan, h->relu_bits[l], nullptr, ldw);
+  }
   return B2_OK;
 }
 
@@ -328,6 +375,7 @@ int sum_gradients(b2_handle* h, size_t begin, size_t count, cudaStream_t st) {
     p.epoch = ++h->p2p_epoch;
     p.ctas_done = h->p2p_ctas_done;
     p.status = h->status_dev;
+    p.wait_ns = h->p2p_wait_ns;
     ++h->launches;
     CK(h, p2p_allreduce_launch(p, h->cfg.comm_sms, st));
     return B2_OK;
@@ -349,6 +397,12 @@ int layer_update(b2_handle* h, int l, cudaStream_t st, bool timed) {
   return B2_OK;
 }
 
+// Element range of the bucket of layers [low, high] in the slabs (`high` first), padding included.
+void bucket_range(const b2_handle* h, int low, int high, size_t* begin, size_t* count) {
+  plan_bucket_slice(h->dw_off.data(), h->dw_pad.data(), low, high, h->cfg.world_size, h->cfg.rank, begin, count,
+                    nullptr, nullptr);
+}
+
 // Sum of the gradients of layers [low, high] (contiguous in the slab, `high` first) over all ranks.
 int bucket_allreduce(b2_handle* h, int low, int high, cudaStream_t st, bool timed) {
   if (!(h->cfg.world_size > 1 && h->cfg.allreduce)) return B2_OK;
@@ -358,6 +412,72 @@ int bucket_allreduce(b2_handle* h, int low, int high, cudaStream_t st, bool time
   int rc = sum_gradients(h, begin, end - begin, st);
   if (rc) return rc;
   if (timed) CK(h, cudaEventRecord(phase_ev(h, low, B2_T_ALLREDUCE, 1), st));
+  return B2_OK;
+}
+
+// The reference's route (mlp_omp.cc:90-146, 240-258) for one bucket, in three calls:
+// reduce-scatter of the gradients (rank r receives the sum of slice r, in place) ...
+int bucket_reduce_scatter(b2_handle* h, int low, int high, cudaStream_t st, bool timed) {
+  size_t begin, count;
+  bucket_range(h, low, high, &begin, &count);
+  const size_t es = esize(h->grad_type), per = count / h->cfg.world_size;
+  char* base = static_cast<char*>(h->dw_slab) + begin * es;
+  if (timed) CK(h, cudaEventRecord(phase_ev(h, low, B2_T_ALLREDUCE, 0), st));
+  NCK(h, nccl_api().ReduceScatter(base, base + (size_t)h->cfg.rank * per * es, per,
+                                  h->grad_type == T_BF16 ? ncclBfloat16 : ncclFloat32, ncclSum, h->comm, st));
+  if (timed) CK(h, cudaEventRecord(phase_ev(h, low, B2_T_ALLREDUCE, 1), st));
+  return B2_OK;
+}
+// ... w = fma(-lr, g, w) on the slice this rank owns (1/world of the bucket's SGD traffic) ...
+int bucket_shard_sgd(b2_handle* h, int low, int high, cudaStream_t st, bool timed) {
+  size_t begin, count;
+  bucket_range(h, low, high, &begin, &count);
+  const size_t per = count / h->cfg.world_size, off = begin + (size_t)h->cfg.rank * per;
+  if (timed) CK(h, cudaEventRecord(phase_ev(h, low, B2_T_WGT_UPDATE, 0), st));
+  CK(h, sgd_launch(h->w_slab + off, static_cast<char*>(h->dw_slab) + off * esize(h->grad_type), h->grad_type,
+                   h->op_type == T_BF16 ? h->w16_slab + off : nullptr, per, h->cfg.lr, h->sms, st));
+  ++h->launches;
+  if (timed) CK(h, cudaEventRecord(phase_ev(h, low, B2_T_WGT_UPDATE, 1), st));
+  if (h->op_type == T_BF16) h->masters_stale = true;
+  return B2_OK;
+}
+// ... and allgather of the updated weights: of the bf16 operand copy in BF16 precision (half the
+// bytes; the fp32 masters stay with their owners), of the fp32 weights otherwise.
+int bucket_allgather(b2_handle* h, int low, int high, cudaStream_t st, bool timed) {
+  size_t begin, count;
+  bucket_range(h, low, high, &begin, &count);
+  const size_t per = count / h->cfg.world_size;
+  if (timed) CK(h, cudaEventRecord(phase_ev(h, low, B2_T_ALLGATHER, 0), st));
+  if (h->op_type == T_BF16) {
+    __nv_bfloat16* base = h->w16_slab + begin;
+    NCK(h, nccl_api().AllGather(base + (size_t)h->cfg.rank * per, base, per, ncclBfloat16, h->comm, st));
+  } else {
+    float* base = h->w_slab + begin;
+    NCK(h, nccl_api().AllGather(base + (size_t)h->cfg.rank * per, base, per, ncclFloat32, h->comm, st));
+  }
+  if (timed) CK(h, cudaEventRecord(phase_ev(h, low, B2_T_ALLGATHER, 1), st));
+  return B2_OK;
+}
+
+// Whether the bucket closed by layer `low` takes the sharded route (else: full sum + full SGD).
+bool bucket_sharded(const b2_handle* h, int low) {
+  return h->shard && !h->bucket_full[low];
+}
+
+// Brings every rank's fp32 master weights up to date (collective; BF16 precision with
+// shard_update only): each rank contributes the slices it owns.
+int gather_masters(b2_handle* h) {
+  if (!h->masters_stale) return B2_OK;
+  for (int l = h->L - 1; l >= 0; --l) {
+    if (h->bucket_low[l] != l || !bucket_sharded(h, l)) continue;
+    size_t begin, count;
+    bucket_range(h, l, h->bucket_high[l], &begin, &count);
+    const size_t per = count / h->cfg.world_size;
+    float* base = h->w_slab + begin;
+    NCK(h, nccl_api().AllGather(base + (size_t)h->cfg.rank * per, base, per, ncclFloat32, h->comm, h->s_main));
+  }
+  CK(h, cudaStreamSynchronize(h->s_main));
+  h->masters_stale = false;
   return B2_OK;
 }
 
@@ -382,6 +502,7 @@ int enqueue_step(b2_handle* h, bool timed, int slot = 0) {
   cudaStream_t su = overlap ? h->s_upd : h->s_main;
   const bool has_ar = h->cfg.world_size > 1 && h->cfg.allreduce;
   int rc;
+  int pending_ag = -1;  // bucket (its lowest layer) whose allgather is still to be issued
   CK(h, cudaMemsetAsync(loss_acc, 0, sizeof(double), sm));
   for (int l = 0; l < L; ++l) {
     if (overlap && h->upd_pending[l]) {
@@ -411,12 +532,29 @@ int enqueue_step(b2_handle* h, bool timed, int slot = 0) {
     }
     if (timed) CK(h, cudaEventRecord(phase_ev(h, l, B2_T_WGT_GRAD, 1), sw));
     const bool closes_bucket = (h->bucket_low[l] == l);
+    const bool sharded = closes_bucket && has_ar && bucket_sharded(h, l);
     if (overlap) {
       CK(h, cudaEventRecord(h->ev_wgrad[l], sw));
       // in-order weight-gradient stream: the event covers every layer of the bucket
       if (closes_bucket) CK(h, cudaStreamWaitEvent(has_ar ? sc : su, h->ev_wgrad[l], 0));
     }
-    if (closes_bucket && has_ar) {
+    if (sharded) {
+      // reduce-scatter of this bucket; behind it, on the same stream, the allgather of the bucket
+      // before (its owned-slice SGD ran while this reduce-scatter was in flight)
+      if ((rc = bucket_reduce_scatter(h, l, h->bucket_high[l], sc, timed))) return rc;
+      if (overlap) CK(h, cudaEventRecord(h->ev_ar[l], sc));
+      if (pending_ag >= 0) {
+        if (overlap) CK(h, cudaStreamWaitEvent(sc, h->ev_shard[pending_ag], 0));
+        if ((rc = bucket_allgather(h, pending_ag, h->bucket_high[pending_ag], sc, timed))) return rc;
+        for (int k = pending_ag; k <= h->bucket_high[pending_ag]; ++k) {
+          if (overlap) {
+            CK(h, cudaEventRecord(h->ev_upd[k], sc));
+            h->upd_pending[k] = 1;
+          }
+        }
+        pending_ag = -1;
+      }
+    } else if (closes_bucket && has_ar) {
       if ((rc = bucket_allreduce(h, l, h->bucket_high[l], sc, timed))) return rc;
       if (overlap) {
         CK(h, cudaEventRecord(h->ev_ar[l], sc));
@@ -427,7 +565,17 @@ int enqueue_step(b2_handle* h, bool timed, int slot = 0) {
     if ((rc = run_site(h, h->dgrad[l], sm))) return rc;
     if (timed) CK(h, cudaEventRecord(phase_ev(h, l, B2_T_BWD, 1), sm));
     if (overlap) CK(h, cudaEventRecord(h->ev_dgrad[l], sm));
-    if (closes_bucket) {
+    if (sharded) {
+      // SGD of the owned slice: after the reduce-scatter and after dgrad(l), the last reader of the
+      // bucket's old weights on the in-order main stream
+      if (overlap) {
+        CK(h, cudaStreamWaitEvent(su, h->ev_ar[l], 0));
+        CK(h, cudaStreamWaitEvent(su, h->ev_dgrad[l], 0));
+      }
+      if ((rc = bucket_shard_sgd(h, l, h->bucket_high[l], su, timed))) return rc;
+      if (overlap) CK(h, cudaEventRecord(h->ev_shard[l], su));
+      pending_ag = l;
+    } else if (closes_bucket) {
       // SGD of every layer of the bucket, on its own stream so that the next bucket's sum does
       // not queue behind it: after this bucket's sum, and after dgrad(l), the last reader of the
       // bucket's old weights on the in-order main stream. Lowest layer first: it is the first
@@ -439,6 +587,16 @@ int enqueue_step(b2_handle* h, bool timed, int slot = 0) {
           CK(h, cudaEventRecord(h->ev_upd[k], su));
           h->upd_pending[k] = 1;
         }
+      }
+    }
+  }
+  if (pending_ag >= 0) {  // the allgather of the last bucket
+    if (overlap) CK(h, cudaStreamWaitEvent(sc, h->ev_shard[pending_ag], 0));
+    if ((rc = bucket_allgather(h, pending_ag, h->bucket_high[pending_ag], sc, timed))) return rc;
+    for (int k = pending_ag; k <= h->bucket_high[pending_ag]; ++k) {
+      if (overlap) {
+        CK(h, cudaEventRecord(h->ev_upd[k], sc));
+        h->upd_pending[k] = 1;
       }
     }
   }
@@ -482,13 +640,16 @@ void free_all(b2_handle* h) {
   for (auto& s : h->fwd) gemm_tc_plan_destroy(s.plan);
   for (auto& s : h->wgrad) gemm_tc_plan_destroy(s.plan);
   for (auto& s : h->dgrad) gemm_tc_plan_destroy(s.plan);
-  for (auto p : h->w) cudaFree(p);
-  for (auto p : h->w16) cudaFree(p);
+  cudaFree(h->w_slab);
+  cudaFree(h->w16_slab);
+  for (auto e : h->ev_shard)
+    if (e) cudaEventDestroy(e);
   for (int r = 0; r < P2P_MAX_RANKS; ++r)
     if (h->p2p_opened[r]) cudaIpcCloseMemHandle(h->p2p_opened[r]);
   cudaFree(h->p2p_ctas_done);
   cudaFree(h->dw_slab);
   for (auto p : h->act) cudaFree(p);
+  for (auto p : h->relu_bits) cudaFree(p);
   for (auto p : h->dz) cudaFree(p);
   cudaFree(h->y);
   cudaFree(h->target);
@@ -509,6 +670,7 @@ void free_all(b2_handle* h) {
   }
   if (h->s_copy) cudaStreamDestroy(h->s_copy);
   cudaFree(h->status_dev);
+  cudaFree(h->fp_dev);
   cudaFree(h->tc_ws);
   cudaFree(h->tc_ws_flags);
   for (auto e : h->ev_wgrad) cudaEventDestroy(e);
@@ -549,6 +711,7 @@ int b2_config_default(b2_config* c) {
   c->input_grad = 1;
   c->comm_sms = -1;
   c->ar_bucket_mb = -1;
+  c->shard_update = -1;
   c->lr = 0.01f;
   return B2_OK;
 }
@@ -670,28 +833,36 @@ int b2_create(const b2_config* cfg, b2_handle** out) {
   h->dw.assign(L, nullptr);
   h->dz.assign(L, nullptr);
   h->act.assign(L + 1, nullptr);
+  h->relu_bits.assign(L + 1, nullptr);
   size_t max_elems = 16;
   for (int l = 0; l < L; ++l) {
     const size_t nw = (size_t)h->nf[l + 1] * h->nf[l];
-    TRY(dev_alloc(h, &h->w[l], nw * 4));
-    if (h->op_type == T_BF16) TRY(dev_alloc(h, &h->w16[l], nw * 2));
-
     TRY(dev_alloc(h, &h->dz[l], bl * h->nf[l + 1] * esize(h->op_type)));
     TRY(dev_alloc(h, &h->act[l], bl * h->nf[l] * esize(h->op_type)));
+    if (l > 0 && cfg->mode == B2_MODE_BASELINE && cfg->precision != B2_PREC_FP32 && !cfg->force_simt &&
+        h->nf[l] % 32 == 0)
+      TRY(dev_alloc(h, &h->relu_bits[l], bl * (size_t)(h->nf[l] / 32) * sizeof(uint32_t)));
     if (nw > max_elems) max_elems = nw;
     if (bl * h->nf[l] > max_elems) max_elems = bl * h->nf[l];
     if (bl * h->nf[l + 1] > max_elems) max_elems = bl * h->nf[l + 1];
   }
   {
-    // gradient slab, last layer first; every layer starts on a 256-byte boundary
+    // gradient and weight slabs, last layer first; every layer is padded to a multiple of
+    // 128 * world elements, so that it starts on a 256-byte boundary in each slab and every
+    // bucket of layers divides evenly among the ranks (the padding stays zero: 0 - lr * 0)
     h->dw_off.assign(L, 0);
-    const size_t es = esize(h->grad_type), align_elems = 256 / es;
-    size_t total = 0;
-    for (int l = L - 1; l >= 0; --l) {
-      h->dw_off[l] = total;
-      const size_t nw = (size_t)h->nf[l + 1] * h->nf[l];
-      total += (nw + align_elems - 1) / align_elems * align_elems;
+    h->dw_pad.assign(L, 0);
+    const size_t es = esize(h->grad_type);
+    std::vector<size_t> layer_elems(L);
+    for (int l = 0; l < L; ++l) layer_elems[l] = (size_t)h->nf[l + 1] * h->nf[l];
+    const size_t total = plan_slab_layout(layer_elems.data(), L, cfg->world_size, h->dw_off.data(), h->dw_pad.data());
+    TRY(dev_alloc(h, &h->w_slab, total * 4));
+    if (h->op_type == T_BF16) TRY(dev_alloc(h, &h->w16_slab, total * 2));
+    for (int l = 0; l < L; ++l) {
+      h->w[l] = h->w_slab + h->dw_off[l];
+      if (h->w16_slab) h->w16[l] = h->w16_slab + h->dw_off[l];
     }
+    h->shard = cfg->world_size > 1 && cfg->allreduce && cfg->shard_update != 0;
     h->p2p_flags_off = (total * es + 255) / 256 * 256;
     h->slab_bytes = h->p2p_flags_off + 256;  // zero-filled flag block (P2P_FLAG_BYTES) behind the gradients
     TRY(dev_alloc(h, &h->dw_slab, h->slab_bytes));
@@ -728,6 +899,7 @@ int b2_create(const b2_config* cfg, b2_handle** out) {
     TRYCK(cudaEventCreateWithFlags(&h->ev_loss[i], cudaEventDisableTiming));
   }
   TRY(dev_alloc(h, &h->status_dev, sizeof(unsigned int)));
+  TRY(dev_alloc(h, &h->fp_dev, sizeof(unsigned long long)));
   if (cfg->precision != B2_PREC_FP32 && !cfg->force_simt) {
     TRY(dev_alloc(h, &h->tc_ws, (size_t)h->sms * TC_WS_SLOT_BYTES));
     TRY(dev_alloc(h, &h->tc_ws_flags, (size_t)h->sms * sizeof(unsigned int)));
@@ -737,8 +909,11 @@ int b2_create(const b2_config* cfg, b2_handle** out) {
   h->ev_dgrad.assign(L, nullptr);
   h->ev_upd.assign(L, nullptr);
   h->ev_ar.assign(L, nullptr);
+  h->ev_shard.assign(L, nullptr);
+  h->bucket_full.assign(L, 0);
   h->upd_pending.assign(L, 0);
   for (int l = 0; l < L; ++l) {
+    TRYCK(cudaEventCreateWithFlags(&h->ev_shard[l], cudaEventDisableTiming));
     TRYCK(cudaEventCreateWithFlags(&h->ev_wgrad[l], cudaEventDisableTiming));
     TRYCK(cudaEventCreateWithFlags(&h->ev_dgrad[l], cudaEventDisableTiming));
     TRYCK(cudaEventCreateWithFlags(&h->ev_upd[l], cudaEventDisableTiming));
@@ -821,6 +996,8 @@ int b2_download_weights(b2_handle* h, int l, float* host, size_t ld) {
   ENTER(h);
   LAYER_OK(h, l, h->L - 1);
   if (!host || ld < (size_t)h->nf[l]) return fail(h, B2_ERR_INVALID, "bad host matrix");
+  int rc = gather_masters(h);  // collective when ranks hold current masters only for their own slices
+  if (rc) return rc;
   return download_matrix(h, h->w[l], T_F32, host, ld, h->nf[l + 1], h->nf[l]);
 }
 
@@ -955,8 +1132,15 @@ int b2_step(b2_handle* h, int iters) {
     if (h->comm) {
       // connect the communicator outside the capture: each bucket's collective once, in place on
       // the gradient slab, whose contents are dead until the step's weight-gradient GEMMs rewrite them
-      for (int l = h->L - 1; l >= 0; --l)
-        if (h->bucket_low[l] == l && (rc = bucket_allreduce(h, l, h->bucket_high[l], h->s_comm, false))) return rc;
+      for (int l = h->L - 1; l >= 0; --l) {
+        if (h->bucket_low[l] != l) continue;
+        if (bucket_sharded(h, l)) {  // the weights of all ranks are equal: gathering them changes nothing
+          if ((rc = bucket_reduce_scatter(h, l, h->bucket_high[l], h->s_comm, false))) return rc;
+          if ((rc = bucket_allgather(h, l, h->bucket_high[l], h->s_comm, false))) return rc;
+        } else if ((rc = bucket_allreduce(h, l, h->bucket_high[l], h->s_comm, false))) {
+          return rc;
+        }
+      }
       CK(h, cudaStreamSynchronize(h->s_comm));
     }
     if ((rc = capture_graph(h))) return rc;
@@ -1119,10 +1303,40 @@ int b2_allreduce_sgd(b2_handle* h, int l) {
   ENTER(h);
   LAYER_OK(h, l, h->L - 1);
   int rc;
-  if ((rc = layer_update(h, l, h->s_main, false))) return rc;
-  if ((rc = layer_sgd(h, l, h->s_main, false))) return rc;
+  const bool has_ar = h->cfg.world_size > 1 && h->cfg.allreduce;
+  if (has_ar && h->bucket_low[l] == l && h->bucket_high[l] == l && bucket_sharded(h, l)) {
+    // the layer is a bucket of its own: the reference's route (mlp_omp.cc:297-323)
+    if ((rc = bucket_reduce_scatter(h, l, l, h->s_main, false))) return rc;
+    if ((rc = bucket_shard_sgd(h, l, l, h->s_main, false))) return rc;
+    if ((rc = bucket_allgather(h, l, l, h->s_main, false))) return rc;
+  } else {
+    // a layer inside a larger bucket: the slices of the ranks follow the bucket, not the layer,
+    // so sum the whole layer everywhere and update it everywhere (needs current masters everywhere)
+    if ((rc = gather_masters(h))) return rc;
+    if ((rc = layer_update(h, l, h->s_main, false))) return rc;
+    if ((rc = layer_sgd(h, l, h->s_main, false))) return rc;
+  }
   CK(h, cudaStreamSynchronize(h->s_main));
-  return B2_OK;
+  return check_status(h);  // a peer-memory sum that gave up must not pass for a result
+}
+
+int b2_allreduce(b2_handle* h, void* dev_buf, size_t count, int dtype) {
+  ENTER(h);
+  if (!dev_buf || count == 0) return fail(h, B2_ERR_INVALID, "bad buffer");
+  if (dtype != B2_DTYPE_F32 && dtype != B2_DTYPE_BF16) return fail(h, B2_ERR_INVALID, "bad dtype");
+  cudaPointerAttributes attr;
+  if (cudaPointerGetAttributes(&attr, dev_buf) != cudaSuccess || attr.type != cudaMemoryTypeDevice ||
+      attr.device != h->cfg.device) {
+    cudaGetLastError();
+    return fail(h, B2_ERR_INVALID, "not a device pointer of GPU %d", h->cfg.device);
+  }
+  if (h->cfg.world_size > 1) {
+    if (!h->comm) return fail(h, B2_ERR_STATE, "the handle was created without a communicator (allreduce = 0)");
+    NCK(h, nccl_api().AllReduce(dev_buf, dev_buf, count, dtype == B2_DTYPE_BF16 ? ncclBfloat16 : ncclFloat32, ncclSum,
+                                h->comm, h->s_main));
+  }
+  CK(h, cudaStreamSynchronize(h->s_main));
+  return check_comm(h);
 }
 
 namespace {
@@ -1196,14 +1410,37 @@ int b2_p2p_connect(b2_handle* h, const void* descs, size_t max_bytes) {
     h->p2p_slab[r] = reinterpret_cast<float*>(base);
     h->p2p_flags[r] = reinterpret_cast<unsigned int*>(base + h->p2p_flags_off);
   }
+  // buckets small enough for the peer path are summed in full on every rank and updated by every
+  // rank from now on (also when the peer path later falls back to NCCL), so bring the masters up
+  // to date first (every rank is in this call)
+  int rc = gather_masters(h);
+  if (rc) return rc;
+  const size_t es = esize(h->grad_type);
+  for (int l = 0; l < h->L; ++l) {
+    if (h->bucket_low[l] != l) continue;
+    const size_t bytes = (h->dw_off[l] + (size_t)h->nf[l + 1] * h->nf[l] - h->dw_off[h->bucket_high[l]]) * es;
+    h->bucket_full[l] = (max_bytes > 0 && bytes <= max_bytes) ? 1 : 0;
+  }
   h->p2p_max_bytes = max_bytes;
   h->p2p_epoch = 0;
   h->p2p_ready = max_bytes > 0;
   return B2_OK;
 }
 
+int b2_p2p_set_wait_ms(b2_handle* h, int ms) {
+  if (!h) return B2_ERR_INVALID;
+  if (ms < 1 || ms > 60000) return fail(h, B2_ERR_INVALID, "wait limit must be 1 .. 60000 ms");
+  h->p2p_wait_ns = (unsigned long long)ms * 1000000ull;
+  return B2_OK;
+}
+
 int b2_p2p_emulate(int device, int world, float* const* bufs, size_t count) {
-  if (world < 2 || world > P2P_MAX_RANKS || !bufs || count == 0)
+  return b2_p2p_emulate_opts(device, world, bufs, count, 1000, -1);
+}
+
+int b2_p2p_emulate_opts(int device, int world, float* const* bufs, size_t count, int wait_ms, int lagging_rank) {
+  if (world < 2 || world > P2P_MAX_RANKS || !bufs || count == 0 || wait_ms < 1 || wait_ms > 60000 ||
+      lagging_rank >= world)
     return fail(nullptr, B2_ERR_INVALID, "bad arguments");
   cudaError_t e = cudaSetDevice(device);
   if (e != cudaSuccess) return fail(nullptr, B2_ERR_CUDA, "cudaSetDevice: %s", cudaGetErrorString(e));
@@ -1232,7 +1469,9 @@ int b2_p2p_emulate(int device, int world, float* const* bufs, size_t count) {
       p.rank = r;
       p.offset = 0;
       p.count = count;
-      p.epoch = 1;
+      // a lagging rank is one call behind the others: it announces call 1 while they wait for call 2
+      p.epoch = (r == lagging_rank) ? 1u : 2u;
+      p.wait_ns = (unsigned long long)wait_ms * 1000000ull;
       p.ctas_done = reinterpret_cast<unsigned int*>(mem + off_cnt) + r;
       p.status = reinterpret_cast<unsigned int*>(mem + off_status);
     }
@@ -1255,14 +1494,18 @@ int b2_p2p_emulate(int device, int world, float* const* bufs, size_t count) {
   return rc;
 }
 
-int b2_allreduce_bench(b2_handle* h, size_t count, int dtype, int warmup, int iters, double* ms_per_iter,
-                       double* checksum) {
+int b2_collective_bench(b2_handle* h, int kind, size_t count, int dtype, int warmup, int iters, double* ms_per_iter,
+                        double* checksum) {
   ENTER(h);
   if (count == 0 || iters < 1 || warmup < 0) return fail(h, B2_ERR_INVALID, "bad sweep arguments");
   if (dtype != B2_DTYPE_F32 && dtype != B2_DTYPE_BF16) return fail(h, B2_ERR_INVALID, "bad dtype");
+  if (kind < 0 || kind > 2) return fail(h, B2_ERR_INVALID, "kind: 0 allreduce, 1 reduce-scatter, 2 allgather");
   const int type = dtype == B2_DTYPE_BF16 ? T_BF16 : T_F32;
   const int ntype = dtype == B2_DTYPE_BF16 ? ncclBfloat16 : ncclFloat32;
-  const bool multi = h->cfg.world_size > 1 && h->comm;
+  const int world = h->cfg.world_size;
+  const bool multi = world > 1 && h->comm;
+  if (kind != 0 && count % (size_t)world != 0) return fail(h, B2_ERR_INVALID, "count must divide by the number of ranks");
+  const size_t per = count / (size_t)world;
   void *src = nullptr, *dst = nullptr;
   CK(h, cudaMalloc(&src, count * esize(type)));
   cudaError_t e = cudaMalloc(&dst, count * esize(type));
@@ -1272,10 +1515,16 @@ int b2_allreduce_bench(b2_handle* h, size_t count, int dtype, int warmup, int it
   }
   int rc = B2_OK;
   auto run = [&]() -> int {
-    if (multi) {
+    if (!multi) return B2_OK;  // one rank: nothing to exchange
+    char* s8 = static_cast<char*>(src);
+    char* d8 = static_cast<char*>(dst);
+    if (kind == 0) {
       NCK(h, nccl_api().AllReduce(src, dst, count, ntype, ncclSum, h->comm, h->s_main));
+    } else if (kind == 1) {
+      NCK(h, nccl_api().ReduceScatter(src, d8 + (size_t)h->cfg.rank * per * esize(type), per, ntype, ncclSum, h->comm,
+                                      h->s_main));
     } else {
-      CK(h, cudaMemcpyAsync(dst, src, count * esize(type), cudaMemcpyDeviceToDevice, h->s_main));
+      NCK(h, nccl_api().AllGather(s8 + (size_t)h->cfg.rank * per * esize(type), dst, per, ntype, h->comm, h->s_main));
     }
     return B2_OK;
   };
@@ -1285,6 +1534,7 @@ int b2_allreduce_bench(b2_handle* h, size_t count, int dtype, int warmup, int it
       break;
     }
     ++h->launches;
+    if (!multi) cudaMemcpyAsync(dst, src, count * esize(type), cudaMemcpyDeviceToDevice, h->s_main);
     for (int i = 0; i < warmup && rc == B2_OK; ++i) rc = run();
     if (rc) break;
     cudaEventRecord(h->ev_t0, h->s_main);
@@ -1292,12 +1542,12 @@ int b2_allreduce_bench(b2_handle* h, size_t count, int dtype, int warmup, int it
     if (rc) break;
     cudaEventRecord(h->ev_t1, h->s_main);
     if (cudaStreamSynchronize(h->s_main) != cudaSuccess) {
-      rc = fail(h, B2_ERR_CUDA, "allreduce sweep: %s", cudaGetErrorString(cudaGetLastError()));
+      rc = fail(h, B2_ERR_CUDA, "collective sweep: %s", cudaGetErrorString(cudaGetLastError()));
       break;
     }
     float ms = 0.f;
     cudaEventElapsedTime(&ms, h->ev_t0, h->ev_t1);
-    if (ms_per_iter) *ms_per_iter = (double)ms / iters;
+    if (ms_per_iter) *ms_per_iter = multi ? (double)ms / iters : 0.0;
     if (checksum) {
       const size_t n = count < 4096 ? count : 4096;
       std::vector<float> host(n);
@@ -1312,9 +1562,184 @@ int b2_allreduce_bench(b2_handle* h, size_t count, int dtype, int warmup, int it
       for (size_t i = 0; i < n; ++i) s += host[i];
       *checksum = s;
     }
+    rc = check_comm(h);
   } while (0);
   cudaFree(src);
   cudaFree(dst);
+  return rc;
+}
+
+int b2_allreduce_bench(b2_handle* h, size_t count, int dtype, int warmup, int iters, double* ms_per_iter,
+                       double* checksum) {
+  return b2_collective_bench(h, 0, count, dtype, warmup, iters, ms_per_iter, checksum);
+}
+
+int b2_sgd_bench(b2_handle* h, size_t nparams, int grad_dtype, int with_bf16_copy, int warmup, int iters,
+                 double* ms_per_iter, double* bytes_per_iter) {
+  ENTER(h);
+  if (nparams == 0 || iters < 1 || warmup < 0) return fail(h, B2_ERR_INVALID, "bad arguments");
+  if (grad_dtype != B2_DTYPE_F32 && grad_dtype != B2_DTYPE_BF16) return fail(h, B2_ERR_INVALID, "bad dtype");
+  const int gt = grad_dtype == B2_DTYPE_BF16 ? T_BF16 : T_F32;
+  const size_t per_param = 4 + esize(gt) + 4 + (with_bf16_copy ? 2 : 0);  // read w, read g, write w (+ write bf16 copy)
+  // parameter sets in rotation, together several times the L2, so that every launch streams from HBM
+  int sets = (int)((size_t(512) << 20) / (nparams * per_param)) + 1;
+  if (sets > 16) sets = 16;
+  if (sets < 2) sets = 2;
+  std::vector<float*> w(sets, nullptr);
+  std::vector<void*> g(sets, nullptr);
+  std::vector<__nv_bfloat16*> w16(sets, nullptr);
+  int rc = B2_OK;
+  do {
+    for (int i = 0; i < sets; ++i) {
+      if (cudaMalloc((void**)&w[i], nparams * 4) != cudaSuccess || cudaMalloc(&g[i], nparams * esize(gt)) != cudaSuccess ||
+          (with_bf16_copy && cudaMalloc((void**)&w16[i], nparams * 2) != cudaSuccess)) {
+        rc = fail(h, B2_ERR_CUDA, "cudaMalloc: %s", cudaGetErrorString(cudaGetLastError()));
+        break;
+      }
+      fill_uniform_launch(w[i], T_F32, nparams, 11 + i, -1.f, 1.f, h->s_main);
+      fill_uniform_launch(g[i], gt, nparams, 31 + i, -1.f, 1.f, h->s_main);
+    }
+    if (rc) break;
+    cudaError_t e = cudaSuccess;
+    for (int i = 0; i < warmup && e == cudaSuccess; ++i)
+      e = sgd_launch(w[i % sets], g[i % sets], gt, w16[i % sets], nparams, 1e-6f, h->sms, h->s_main);
+    if (e == cudaSuccess) e = cudaEventRecord(h->ev_t0, h->s_main);
+    for (int i = 0; i < iters && e == cudaSuccess; ++i) {
+      e = sgd_launch(w[(warmup + i) % sets], g[(warmup + i) % sets], gt, w16[(warmup + i) % sets], nparams, 1e-6f,
+                     h->sms, h->s_main);
+      ++h->launches;
+    }
+    if (e == cudaSuccess) e = cudaEventRecord(h->ev_t1, h->s_main);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(h->s_main);
+    if (e != cudaSuccess) {
+      rc = fail(h, B2_ERR_CUDA, "SGD benchmark: %s", cudaGetErrorString(e));
+      break;
+    }
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, h->ev_t0, h->ev_t1);
+    if (ms_per_iter) *ms_per_iter = (double)ms / iters;
+    if (bytes_per_iter) *bytes_per_iter = (double)(nparams * per_param);
+  } while (0);
+  for (int i = 0; i < sets; ++i) {
+    cudaFree(w[i]); cudaFree(g[i]); cudaFree(w16[i]);
+  }
+  return rc;
+}
+
+int b2_set_timing(b2_handle* h, int collect_timing) {
+  if (!h) return B2_ERR_INVALID;
+  if (h->async_issued != h->async_waited) return fail(h, B2_ERR_STATE, "pipelined steps in flight");
+  h->cfg.collect_timing = collect_timing ? 1 : 0;
+  return B2_OK;
+}
+
+int b2_weights_fingerprint(b2_handle* h, int l, unsigned long long* out) {
+  ENTER(h);
+  LAYER_OK(h, l, h->L - 1);
+  if (!out) return fail(h, B2_ERR_INVALID, "null output");
+  unsigned long long* acc = h->fp_dev;
+  const size_t n = (size_t)h->nf[l + 1] * h->nf[l];
+  CK(h, cudaStreamSynchronize(h->s_main));
+  CK(h, cudaMemsetAsync(acc, 0, sizeof *acc, h->s_main));
+  if (h->op_type == T_BF16)
+    CK(h, fingerprint_launch(h->w16[l], n * 2, acc, h->s_main));
+  else
+    CK(h, fingerprint_launch(h->w[l], n * 4, acc, h->s_main));
+  ++h->launches;
+  CK(h, cudaMemcpyAsync(out, acc, sizeof *out, cudaMemcpyDeviceToHost, h->s_main));
+  CK(h, cudaStreamSynchronize(h->s_main));
+  return B2_OK;
+}
+
+int b2_gemm_bench(b2_handle* h, int form, int m, int n, int k, int precision, int epilogue, int out_dtype, int sms,
+                  int warmup, int iters, double* ms_per_iter) {
+  ENTER(h);
+  if (form < 0 || form > 2 || m < 1 || n < 1 || k < 1 || iters < 1 || warmup < 0)
+    return fail(h, B2_ERR_INVALID, "bad GEMM benchmark arguments");
+  if (precision != B2_PREC_TF32 && precision != B2_PREC_BF16 && precision != B2_PREC_FP32)
+    return fail(h, B2_ERR_INVALID, "unknown precision %d", precision);
+  if (epilogue < EPI_NONE || epilogue > EPI_MASK) return fail(h, B2_ERR_INVALID, "bad epilogue");
+  const int in_type = precision == B2_PREC_BF16 ? T_BF16 : T_F32;
+  const int out_type = out_dtype == B2_DTYPE_BF16 ? T_BF16 : T_F32;
+  if (out_type == T_BF16 && in_type != T_BF16) return fail(h, B2_ERR_INVALID, "bf16 output needs BF16 precision");
+  const size_t ea = (size_t)m * k, eb = (size_t)k * n, ec = (size_t)m * n;
+  const size_t set_bytes = (ea + eb) * esize(in_type) + ec * esize(out_type) + (epilogue != EPI_NONE ? ec * esize(in_type) : 0);
+  // operand sets used in rotation so that consecutive launches find nothing of theirs in the L2
+  int sets = (int)((size_t(384) << 20) / set_bytes) + 1;
+  if (sets > 16) sets = 16;
+  if (sets < 1) sets = 1;
+  struct Set { void *a, *b, *c, *x; TcPlan* plan; GemmDesc d; };
+  std::vector<Set> S(sets, Set{nullptr, nullptr, nullptr, nullptr, nullptr, GemmDesc{}});
+  int rc = B2_OK;
+  const bool tc = precision != B2_PREC_FP32 && !h->cfg.force_simt;
+  do {
+    for (int i = 0; i < sets && rc == B2_OK; ++i) {
+      Set& s = S[i];
+      if (cudaMalloc(&s.a, ea * esize(in_type)) != cudaSuccess || cudaMalloc(&s.b, eb * esize(in_type)) != cudaSuccess ||
+          cudaMalloc(&s.c, ec * esize(out_type)) != cudaSuccess ||
+          (epilogue != EPI_NONE && cudaMalloc(&s.x, ec * esize(in_type)) != cudaSuccess)) {
+        rc = fail(h, B2_ERR_CUDA, "cudaMalloc: %s", cudaGetErrorString(cudaGetLastError()));
+        break;
+      }
+      fill_uniform_launch(s.a, in_type, ea, 7 + 3 * i, -1.f, 1.f, h->s_main);
+      fill_uniform_launch(s.b, in_type, eb, 8 + 3 * i, -1.f, 1.f, h->s_main);
+      if (s.x) fill_uniform_launch(s.x, in_type, ec, 9 + 3 * i, -1.f, 1.f, h->s_main);
+      GemmDesc& d = s.d;
+      d.M = m; d.N = n; d.K = k;
+      d.A = s.a; d.B = s.b; d.C = s.c; d.ldc = n;
+      if (form == 0) {         // forward: A m x k, B n x k
+        d.sAm = k; d.sAk = 1; d.sBk = 1; d.sBn = k;
+      } else if (form == 1) {  // weight gradient: A stored k x m, B stored k x n
+        d.sAm = 1; d.sAk = m; d.sBk = n; d.sBn = 1;
+      } else {                 // input gradient: A m x k, B k x n
+        d.sAm = k; d.sAk = 1; d.sBk = n; d.sBn = 1;
+      }
+      d.aux = s.x; d.ldaux = n;
+      d.alpha = 1.f; d.beta = 0.f;
+      d.epilogue = epilogue;
+      d.in_type = in_type; d.out_type = out_type;
+      d.ws = nullptr; d.ws_flags = nullptr;
+      if (tc) {
+        char why[128] = "";
+        s.plan = gemm_tc_plan_create(d, sms > 0 && sms <= h->sms ? sms : h->sms, why, sizeof why);
+        if (!s.plan) rc = fail(h, B2_ERR_UNSUPPORTED, "tensor-core kernel refuses this GEMM: %s", why);
+        // like the step: the ReLU bit plane (here: the first bytes of the auxiliary buffer) is written
+        // by a forward epilogue and read by an input-gradient epilogue instead of the activation
+        if (s.plan && n % 32 == 0 && epilogue == EPI_RELU)
+          gemm_tc_plan_set_mask(s.plan, static_cast<uint32_t*>(s.x), nullptr, n / 32);
+        if (s.plan && n % 32 == 0 && epilogue == EPI_MASK)
+          gemm_tc_plan_set_mask(s.plan, nullptr, static_cast<const uint32_t*>(s.x), n / 32);
+      }
+    }
+    if (rc) break;
+    auto run = [&](int i) -> cudaError_t {
+      Set& s = S[i % sets];
+      ++h->launches;
+      if (s.plan) {
+        ++h->tc_launches;
+        return gemm_tc_launch(s.plan, h->s_main, h->status_dev);
+      }
+      return gemm_simt_launch(s.d, h->s_main);
+    };
+    cudaError_t e = cudaSuccess;
+    for (int i = 0; i < warmup && e == cudaSuccess; ++i) e = run(i);
+    if (e == cudaSuccess) e = cudaEventRecord(h->ev_t0, h->s_main);
+    for (int i = 0; i < iters && e == cudaSuccess; ++i) e = run(warmup + i);
+    if (e == cudaSuccess) e = cudaEventRecord(h->ev_t1, h->s_main);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(h->s_main);
+    if (e != cudaSuccess) {
+      rc = fail(h, B2_ERR_CUDA, "GEMM benchmark: %s", cudaGetErrorString(e));
+      break;
+    }
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, h->ev_t0, h->ev_t1);
+    if (ms_per_iter) *ms_per_iter = (double)ms / iters;
+    rc = check_status(h);
+  } while (0);
+  for (auto& s : S) {
+    gemm_tc_plan_destroy(s.plan);
+    cudaFree(s.a); cudaFree(s.b); cudaFree(s.c); cudaFree(s.x);
+  }
   return rc;
 }
 
@@ -1331,9 +1756,9 @@ int b2_write_trace(b2_handle* h, const char* path) {
   if (h->trace.empty()) return fail(h, B2_ERR_STATE, "no timed step recorded (needs collect_timing = 1)");
   FILE* f = fopen(path, "w");
   if (!f) return fail(h, B2_ERR_INVALID, "cannot open %s", path);
-  static const char* names[B2_T_NUM] = {"fwd", "wgt_grad", "bwd", "wgt_update", "allreduce"};
+  static const char* names[B2_T_NUM] = {"fwd", "wgt_grad", "bwd", "wgt_update", "allreduce", "allgather"};
   // one "thread" per stream: main (fwd, bwd), weight-gradient stream, collective stream, update stream
-  static const int tid[B2_T_NUM] = {0, 1, 0, 3, 2};
+  static const int tid[B2_T_NUM] = {0, 1, 0, 3, 2, 2};
   fprintf(f, "[\n");
   for (size_t i = 0; i < h->trace.size(); ++i) {
     const auto& e = h->trace[i];

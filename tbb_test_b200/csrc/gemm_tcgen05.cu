@@ -12,8 +12,11 @@
 //               N = BN, 32 bytes of K per instruction) into one of two TMEM
 //               accumulators and commits stage / accumulator completion to mbarriers
 //   warps 2-5   epilogue: tcgen05.ld the finished accumulator (each warp its own
-//               32-lane quarter), apply ReLU / ReLU-mask / scaling, convert and
-//               store; runs while the MMA warp works on the next tile
+//               32-lane quarter), apply ReLU / ReLU-mask / scaling, convert, stage
+//               128-byte-wide chunks in swizzled shared memory and write them with
+//               TMA stores (coalesced, asynchronous, clipped at the matrix edge);
+//               the accumulator is handed back to the MMA warp as soon as the last
+//               chunk has left TMEM, while the stores are still draining
 //
 // Operand layouts.  Row-major storage gives a K-contiguous ("K-major") operand
 // only for the forward GEMM; the input-gradient GEMM reads W with N contiguous
@@ -86,6 +89,16 @@ struct TcParams {
   int out_bf16, aux_bf16, epilogue;
   float alpha;
   unsigned int* status;
+  // Epilogue through shared memory + TMA stores (tensor map of C as third kernel argument):
+  // every epilogue warp owns epi_bufs chunk buffers of 32 rows x 128 bytes behind the stages.
+  int tma_store, epi_bufs;
+  uint32_t epi_off;  // byte offset of the chunk buffers from the (aligned) start of shared memory
+  // ReLU bit planes: one bit per element, row-major words of 32 columns. A forward epilogue
+  // writes the plane of the activation it produces, the input-gradient epilogue of the layer
+  // above reads it instead of the activation itself (1/16 of the bytes, one word per lane).
+  uint32_t* mask_out;
+  const uint32_t* mask_in;
+  long long ld_mask;  // words per row
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -142,6 +155,21 @@ __device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint64_t* ba
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(smem_u32(src)), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// waits until at most N of this thread's bulk groups still READ their shared-memory source
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -374,6 +402,136 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, int row, bool 
   }
 }
 
+
+// ---- epilogue through shared memory and TMA stores
+//
+// 32 accumulator columns of one row (this lane's), in place: scale, ReLU (returning the bits
+// of the stored value being positive) or masking by `mask` (bit j = keep column j).
+__device__ __forceinline__ void epilogue_math32(const TcParams& p, uint32_t (&r)[32], uint32_t mask) {
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    float v = __uint_as_float(r[j]) * p.alpha;
+    if (p.epilogue == EPI_RELU) {
+      v = v > 0.f ? v : 0.f;
+    } else if (p.epilogue == EPI_MASK) {
+      v = (mask >> j) & 1u ? v : 0.f;
+    }
+    r[j] = __float_as_uint(v);
+  }
+}
+// mask word of 32 columns from the stored activation itself (callers without a bit plane)
+__device__ __forceinline__ uint32_t mask_from_values(const TcParams& p, int row, int col0) {
+  uint32_t m = 0;
+  if (row >= p.M) return 0;
+  if (p.aux_bf16) {
+    const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(p.aux) + (long long)row * p.ldaux + col0;
+    if (col0 + 32 <= p.N) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint4 u = __ldg(reinterpret_cast<const uint4*>(x) + j);
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const uint32_t lo = w[t] & 0xFFFFu, hi = w[t] >> 16;  // positive: non-zero, sign clear
+          if (lo != 0 && lo < 0x8000u) m |= 1u << (j * 8 + t * 2);
+          if (hi != 0 && hi < 0x8000u) m |= 1u << (j * 8 + t * 2 + 1);
+        }
+      }
+    } else {
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N && __bfloat162float(x[j]) > 0.f) m |= 1u << j;
+    }
+  } else {
+    const float* x = static_cast<const float*>(p.aux) + (long long)row * p.ldaux + col0;
+    if (col0 + 32 <= p.N) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float4 u = __ldg(reinterpret_cast<const float4*>(x) + j);
+        if (u.x > 0.f) m |= 1u << (j * 4);
+        if (u.y > 0.f) m |= 1u << (j * 4 + 1);
+        if (u.z > 0.f) m |= 1u << (j * 4 + 2);
+        if (u.w > 0.f) m |= 1u << (j * 4 + 3);
+      }
+    } else {
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N && x[j] > 0.f) m |= 1u << j;
+    }
+  }
+  return m;
+}
+
+// One epilogue warp's 32 rows of one accumulator: rows row0 .. row0+31 (this lane: row0 + lane),
+// columns n0 .. n0 + block_n of C, accumulator at TMEM address `taddr` (lane quarter and first
+// column already applied). `release()` hands the accumulator back to the MMA warp; it is called
+// once, right after the last chunk has been read out of TMEM. `buf` = this warp's chunk
+// buffers (EPI_BUFS x 4 KB, 1024-byte aligned), `buf_i` = the one to use next (kept between tiles).
+template <int EPI_BUFS, typename Release>
+__device__ __forceinline__ void epilogue_rows_tma(const TcParams& p, const CUtensorMap* tma_c, uint32_t taddr,
+                                                  int row0, int n0, uint8_t* buf, int& buf_i, int lane,
+                                                  Release release) {
+  const int row = row0 + lane;
+  const int chunk_cols = p.out_bf16 ? 64 : 32;  // 128 bytes of C per row and chunk
+  const int nchunks = p.block_n / chunk_cols;
+  const uint32_t swz = (uint32_t)(lane & 7);
+  for (int ch = 0; ch < nchunks; ++ch) {
+    const int col0 = n0 + ch * chunk_cols;
+    if (col0 >= p.N) break;  // uniform across the warp
+    const bool last = (ch == nchunks - 1) || (col0 + chunk_cols >= p.N);
+    uint32_t words[32];  // the chunk's 128 bytes of this row
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      if (half == 1 && !p.out_bf16) break;
+      const int c0 = col0 + half * 32;
+      uint32_t r[32];
+      tmem_ld32(taddr + (uint32_t)(ch * chunk_cols + half * 32), r);
+      if (last && (half == 1 || !p.out_bf16)) {
+        tc_fence_before();
+        __syncwarp();
+        release();
+      }
+      uint32_t mask = 0;
+      if (p.epilogue == EPI_MASK) {
+        if (p.mask_in) mask = (row < p.M && c0 < p.N) ? __ldg(p.mask_in + (long long)row * p.ld_mask + (c0 >> 5)) : 0u;
+        else mask = c0 < p.N ? mask_from_values(p, row, c0) : 0u;
+      }
+      epilogue_math32(p, r, mask);
+      uint32_t bits = 0;
+      if (p.out_bf16) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const uint32_t w = pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+          words[half * 16 + j] = w;
+          const uint32_t lo = w & 0xFFFFu, hi = w >> 16;
+          if (lo != 0 && lo < 0x8000u) bits |= 1u << (2 * j);
+          if (hi != 0 && hi < 0x8000u) bits |= 1u << (2 * j + 1);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          words[j] = r[j];
+          if (__uint_as_float(r[j]) > 0.f) bits |= 1u << j;
+        }
+      }
+      if (p.mask_out && row < p.M && c0 < p.N) p.mask_out[(long long)row * p.ld_mask + (c0 >> 5)] = bits;
+    }
+    // the chunk buffer is free once the store issued EPI_BUFS chunks ago has read it
+    if (lane == 0) bulk_wait_read<EPI_BUFS - 1>();
+    __syncwarp();
+    uint8_t* dst = buf + (size_t)buf_i * 4096 + (size_t)lane * 128;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)  // 16-byte piece j of row `lane` sits at slot j ^ (lane & 7): 128-byte swizzle
+      *reinterpret_cast<uint4*>(dst + ((j ^ swz) << 4)) =
+          make_uint4(words[4 * j], words[4 * j + 1], words[4 * j + 2], words[4 * j + 3]);
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0 && row0 < p.M) {
+      tma_store_2d(tma_c, buf + (size_t)buf_i * 4096, col0, row0);
+      bulk_commit();
+    }
+    buf_i = (buf_i + 1 == EPI_BUFS) ? 0 : buf_i + 1;
+  }
+}
+
 // Piece of work of one CTA: k-blocks [kb0, kb1) of one tile (all of them unless stream-K
 // cut the tile).
 struct Work {
@@ -441,7 +599,7 @@ __device__ __forceinline__ void epilogue_bar_sync(int nthreads) {
 template <int SUB_M>
 __global__ void __launch_bounds__(SUB_M == 2 ? NUM_THREADS_SUB2 : NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-               const __grid_constant__ TcParams p) {
+               const __grid_constant__ CUtensorMap tma_c, const __grid_constant__ TcParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[MAX_STAGES];
   __shared__ __align__(8) uint64_t empty_bar[MAX_STAGES];
@@ -468,6 +626,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tma_a) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tma_b) : "memory");
+    if (p.tma_store) asm volatile("prefetch.tensormap [%0];" ::"l"(&tma_c) : "memory");
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)),
@@ -572,13 +731,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     int acc = 0;
     uint32_t acc_phase = 0;
     constexpr int EPI_THREADS = 128 * SUB_M;
+    constexpr int EPI_BUFS = SUB_M == 2 ? 1 : 2;  // chunk buffers per warp (shared memory left beside the stages)
     const int sub = (warp - 2) >> 2;  // each group of four epilogue warps drains one 128-row accumulator
+    uint8_t* ebuf = smem + p.epi_off + (size_t)(warp - 2) * (EPI_BUFS * 4096);
+    int ebuf_i = 0;
     WorkIter wi;
     Work it;
     work_begin(p, wi);
     while (work_next<SUB_M>(p, wi, it)) {
       const int n_blk = it.n_blk;
       const int KB = p.num_k_blocks;
+      if (p.tma_store) {  // whole tiles only (no stream-K pieces)
+        if (!mbar_wait(&acc_full_bar[acc], acc_phase, abort_flag, p.status, 4u)) break;
+        tc_fence_after();
+        uint64_t* release_bar = &acc_empty_bar[acc];
+        if (sub < it.sub) {
+          epilogue_rows_tma<EPI_BUFS>(
+              p, &tma_c,
+              tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * acc_cols + (uint32_t)(sub * p.block_n),
+              it.m0 + sub * BLOCK_M + q * 32, n_blk * p.block_n, ebuf, ebuf_i, lane,
+              [&]() { if (lane == 0) mbar_arrive(release_bar); });
+        } else {  // half tile: this group's accumulator was not used
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(release_bar);
+        }
+        if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
+        continue;
+      }
       const bool contributor = it.kb0 > 0;                 // stream-K: someone else owns this tile
       const bool owner_partial = it.kb0 == 0 && it.kb1 < KB;  // stream-K: others finish this tile
       const long long tile_end = it.unit0 - it.kb0 + KB;
@@ -651,6 +831,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
       if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
     }
+    if (p.tma_store && lane == 0) bulk_wait_all();  // the chunk buffers must outlive the stores that read them
   }
 
   __syncwarp();
@@ -681,7 +862,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 // shared memory and TMEM alive while the other may still touch it.
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                    const __grid_constant__ TcParams p) {
+                    const __grid_constant__ CUtensorMap tma_c, const __grid_constant__ TcParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[MAX_STAGES];
   __shared__ __align__(8) uint64_t empty_bar[MAX_STAGES];
@@ -710,6 +891,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tma_a) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tma_b) : "memory");
+    if (p.tma_store) asm volatile("prefetch.tensormap [%0];" ::"l"(&tma_c) : "memory");
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)),
@@ -802,10 +984,21 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     const int q = warp & 3;
     int acc = 0;
     uint32_t acc_phase = 0;
+    uint8_t* ebuf = smem + p.epi_off + (size_t)(warp - 2) * (2 * 4096);
+    int ebuf_i = 0;
     for (int t = pair; t < num_tiles; t += num_pairs) {
       const Item it = decode_item<2>(t, num_tiles, p.num_m_blocks, p.num_n_blocks, p.raster_m, 1 << 30);
       if (!mbar_wait(&acc_full_bar[acc], acc_phase, abort_flag, p.status, 4u)) break;
       tc_fence_after();
+      if (p.tma_store) {
+        const uint32_t release_addr = map_to_cta(smem_u32(&acc_empty_bar[acc]), 0);
+        epilogue_rows_tma<2>(p, &tma_c, tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * p.block_n),
+                             it.m0 + (int)rank * BLOCK_M + q * 32, it.n_blk * p.block_n, ebuf, ebuf_i, lane,
+                             [&]() { if (lane == 0) mbar_arrive_cluster(release_addr); });
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+        continue;
+      }
       const int row = it.m0 + (int)rank * BLOCK_M + q * 32 + lane;
       const bool row_ok = row < p.M;
       for (int c0 = 0; c0 < p.block_n; c0 += 32) {
@@ -821,6 +1014,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
+    if (p.tma_store && lane == 0) bulk_wait_all();
   }
 
   __syncwarp();
@@ -872,7 +1066,7 @@ bool make_map(CUtensorMap* map, const void* base, int elem_bytes, long long inne
 }  // namespace
 
 struct TcPlan {
-  CUtensorMap map_a, map_b;
+  CUtensorMap map_a, map_b, map_c;
   TcParams p;
   int grid;
   size_t smem;
@@ -904,17 +1098,46 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
   memset(&p, 0, sizeof p);
   p.M = g.M; p.N = g.N; p.K = g.K;
   p.block_k = SLAB_BYTES / eb;
-  // Tile width: the widest of 256/128/64 that still gives every SM a tile.
-  int bn = 256;
+  // Tile shape: 256 x 256 (two 128-row accumulators sharing each B slab: least shared-memory
+  // traffic per flop, but a single accumulator stage), 128 x 256, 128 x 128 or 128 x 64 (two
+  // accumulator stages). Chosen by a cost model: waves of the persistent grid times the time
+  // of one tile, where a tile's time is its area divided by the rate the tile shape sustains
+  // relative to 256 x 256 (measured at 8192 x 4096 x 4096: 128 x 256 reaches 0.93 of it; a
+  // 128-column MMA reads A and B from shared memory at the 128 B/clk ceiling, 0.70; 64 columns
+  // 0.45). Filling every SM is not the goal: 1024 x 4096 is served faster by 128 tiles of
+  // 128 x 256 on 128 SMs than by 256 tiles of 128 x 128 on all 148.
   auto tiles = [&](int rows, int n) { return (long long)((g.M + rows - 1) / rows) * ((g.N + n - 1) / n); };
-  while (bn > 64 && (tiles(BLOCK_M, bn) < sm_count || bn / 2 >= g.N)) bn /= 2;
+  int bn = 256;
+  {
+    struct Cand { int sub_m, bn; double rate; };
+    const Cand cands[4] = {{2, 256, 1.0}, {1, 256, 0.93}, {1, 128, 0.70}, {1, 64, 0.45}};
+    double best = 1e300;
+    int best_i = 3;
+    for (int i = 0; i < 4; ++i) {
+      const Cand& c = cands[i];
+      if (c.bn / 2 >= g.N && c.bn > 64) continue;  // tile wider than twice the matrix
+      const long long T = tiles(c.sub_m * BLOCK_M, c.bn);
+      double waves;
+      if (c.sub_m == 2) {
+        // the last partial wave is handed out as 128-row halves when that fits in one wave
+        const long long full = T / sm_count, rem = T % sm_count;
+        waves = (double)full + (rem == 0 ? 0.0 : (T > sm_count && rem * 2 <= sm_count ? 0.5 : 1.0));
+      } else {
+        waves = (double)((T + sm_count - 1) / sm_count);
+      }
+      const double cost = waves * (double)(c.sub_m * BLOCK_M) * c.bn / c.rate;
+      if (cost < best * 0.999) { best = cost; best_i = i; }
+    }
+    bn = cands[best_i].bn;
+    p.sub_m = cands[best_i].sub_m;
+  }
   p.block_n = bn;
-  // 256-row tiles (two accumulators sharing each B slab: a third less shared-memory
-  // fill traffic per flop, at the price of a single TMEM stage) once they still give
-  // every SM work; 128-row tiles with two TMEM stages otherwise.
   const char* force = getenv("B2_TC_SUB_M");
-  p.sub_m = (bn == 256 && tiles(2 * BLOCK_M, bn) >= sm_count) ? 2 : 1;
   if (force && (force[0] == '1' || (force[0] == '2' && bn == 256))) p.sub_m = force[0] - '0';
+  if (const char* fb = getenv("B2_TC_BN")) {  // experiments: force the tile width
+    const int v = atoi(fb);
+    if (v == 64 || v == 128 || v == 256) { bn = v; p.block_n = v; if (v != 256) p.sub_m = 1; }
+  }
   // CTA pairs: a 256 x 256 tile per pair of SMs once there is a tile for every pair
   {
     const char* pe = getenv("B2_TC_PAIR");
@@ -1016,19 +1239,48 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
     delete plan;
     return fail("cuTensorMapEncodeTiled failed");
   }
+  // Epilogue chunk buffers (32 rows x 128 bytes per buffer) behind the stages: one buffer per
+  // epilogue warp in the 256-row mode (eight warps; three 64 KB stages fill the rest), two otherwise.
+  memset(&plan->map_c, 0, sizeof plan->map_c);
+  {
+    const char* e = getenv("B2_TC_TMA_STORE");
+    p.tma_store = (!p.streamk && !(e && e[0] == '0')) ? 1 : 0;
+    if (p.tma_store) {
+      EncodeTiledFn enc = get_encode();
+      cuuint64_t dims[2] = {(cuuint64_t)g.N, (cuuint64_t)g.M};
+      cuuint64_t strides[1] = {(cuuint64_t)g.ldc * ob};
+      cuuint32_t box[2] = {(cuuint32_t)(128 / ob), 32};
+      cuuint32_t estr[2] = {1, 1};
+      if (!enc || enc(&plan->map_c, ob == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+                      g.C, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                      CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        p.tma_store = 0;  // e.g. a row pitch beyond the tensor map's limits: direct stores serve it
+    }
+  }
+  p.epi_bufs = (p.sub_m == 2 && !p.pair) ? 1 : 2;
+  const size_t epi_bytes = p.tma_store ? (size_t)(p.pair ? 4 : 4 * p.sub_m) * p.epi_bufs * 4096 : 0;
   const size_t stage = p.a_stage_bytes + p.b_stage_bytes;
-  int stages = (int)((200 * 1024) / stage);
+  const size_t budget = 227 * 1024 - 1024 /* alignment slack */ - 512 /* static: barriers */;
+  int stages = (int)((budget - epi_bytes) / stage);
   if (stages > MAX_STAGES) stages = MAX_STAGES;
+  if (stages < 2) {
+    delete plan;
+    return fail("tile does not fit in shared memory");
+  }
   p.stages = stages;
+  p.epi_off = (uint32_t)((size_t)stages * stage);
   // Always ask for the same large carve-out so that only one CTA (one TMEM
   // allocation) is ever resident per SM.
-  plan->smem = 1024 + (size_t)stages * stage;
+  plan->smem = 1024 + (size_t)stages * stage + epi_bytes;
   if (plan->smem < 140 * 1024) plan->smem = 140 * 1024;
   p.C = g.C; p.ldc = g.ldc; p.aux = g.aux; p.ldaux = g.ldaux;
   p.out_bf16 = g.out_type == T_BF16;
   p.aux_bf16 = g.in_type == T_BF16;
   p.epilogue = g.epilogue;
   p.alpha = g.alpha;
+  p.mask_out = nullptr;
+  p.mask_in = nullptr;
+  p.ld_mask = 0;
   plan->grid = p.num_items < sm_count ? p.num_items : sm_count;
   if (p.streamk) plan->grid = sm_count;
   if (p.pair) {
@@ -1041,14 +1293,24 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
 
 void gemm_tc_plan_destroy(TcPlan* p) { delete p; }
 
+bool gemm_tc_plan_set_mask(TcPlan* plan, uint32_t* mask_out, const uint32_t* mask_in, long long ld_words) {
+  if (!plan || !plan->p.tma_store || plan->p.N % 32 != 0 || ld_words * 32 < plan->p.N) return false;
+  if (mask_out && plan->p.epilogue != EPI_RELU) return false;
+  if (mask_in && plan->p.epilogue != EPI_MASK) return false;
+  plan->p.mask_out = mask_out;
+  plan->p.mask_in = mask_in;
+  plan->p.ld_mask = ld_words;
+  return true;
+}
+
 cudaError_t gemm_tc_launch(const TcPlan* plan, cudaStream_t stream, unsigned int* status) {
   static unsigned long long attr_set = 0;  // one bit per device ordinal
   int dev = 0;
   cudaGetDevice(&dev);
   if (!(attr_set >> (dev & 63) & 1ull)) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(gemm_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
+      e = cudaFuncSetAttribute(gemm_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
     if (e != cudaSuccess) return e;
     attr_set |= 1ull << (dev & 63);
   }
@@ -1057,7 +1319,7 @@ cudaError_t gemm_tc_launch(const TcPlan* plan, cudaStream_t stream, unsigned int
   if (p.pair) {
     static unsigned long long pair_attr_set = 0;
     if (!(pair_attr_set >> (dev & 63) & 1ull)) {
-      cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
+      cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
       if (e != cudaSuccess) return e;
       pair_attr_set |= 1ull << (dev & 63);
     }
@@ -1073,12 +1335,12 @@ cudaError_t gemm_tc_launch(const TcPlan* plan, cudaStream_t stream, unsigned int
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel, plan->map_a, plan->map_b, p);
+    return cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel, plan->map_a, plan->map_b, plan->map_c, p);
   }
   if (p.sub_m == 2)
-    gemm_tc_kernel<2><<<plan->grid, NUM_THREADS_SUB2, plan->smem, stream>>>(plan->map_a, plan->map_b, p);
+    gemm_tc_kernel<2><<<plan->grid, NUM_THREADS_SUB2, plan->smem, stream>>>(plan->map_a, plan->map_b, plan->map_c, p);
   else
-    gemm_tc_kernel<1><<<plan->grid, NUM_THREADS, plan->smem, stream>>>(plan->map_a, plan->map_b, p);
+    gemm_tc_kernel<1><<<plan->grid, NUM_THREADS, plan->smem, stream>>>(plan->map_a, plan->map_b, plan->map_c, p);
   return cudaGetLastError();
 }
 

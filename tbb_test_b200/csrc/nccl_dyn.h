@@ -6,7 +6,6 @@
 
 #include <cuda_runtime.h>
 #include <dlfcn.h>
-#include <glob.h>
 #include <stddef.h>
 
 #include <mutex>
@@ -46,6 +45,8 @@ struct NcclApi {
   int (*CommDestroy)(ncclComm_t) = nullptr;
   int (*CommAbort)(ncclComm_t) = nullptr;
   int (*AllReduce)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+  int (*ReduceScatter)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+  int (*AllGather)(const void*, void*, size_t, int, ncclComm_t, cudaStream_t) = nullptr;
   int (*CommGetAsyncError)(ncclComm_t, int*) = nullptr;
   const char* (*GetErrorString)(int) = nullptr;
   int (*GetVersion)(int*) = nullptr;
@@ -66,18 +67,6 @@ inline NcclApi& nccl_api() {
       h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD | RTLD_GLOBAL);
       if (h) api.path = "libnccl.so.2 (already loaded)";
     }
-    const char* pats[] = {"/opt/*/.venv/lib/python3*/site-packages/nvidia/nccl/lib/libnccl.so.2",
-                          "/usr/lib/x86_64-linux-gnu/libnccl.so.2", "/usr/local/cuda/lib64/libnccl.so.2"};
-    for (size_t i = 0; i < sizeof(pats) / sizeof(pats[0]) && !h; ++i) {
-      glob_t g;
-      if (glob(pats[i], 0, nullptr, &g) == 0) {
-        for (size_t j = 0; j < g.gl_pathc && !h; ++j) {
-          h = dlopen(g.gl_pathv[j], RTLD_NOW | RTLD_GLOBAL);
-          if (h) api.path = g.gl_pathv[j];
-        }
-      }
-      globfree(&g);
-    }
     if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
     if (!h) {
       api.error = "libnccl.so.2 not found (set B2_NCCL_PATH)";
@@ -90,10 +79,13 @@ inline NcclApi& nccl_api() {
     api.CommDestroy = (decltype(api.CommDestroy))sym("ncclCommDestroy");
     api.CommAbort = (decltype(api.CommAbort))sym("ncclCommAbort");
     api.AllReduce = (decltype(api.AllReduce))sym("ncclAllReduce");
+    api.ReduceScatter = (decltype(api.ReduceScatter))sym("ncclReduceScatter");
+    api.AllGather = (decltype(api.AllGather))sym("ncclAllGather");
     api.CommGetAsyncError = (decltype(api.CommGetAsyncError))sym("ncclCommGetAsyncError");
     api.GetErrorString = (decltype(api.GetErrorString))sym("ncclGetErrorString");
     api.GetVersion = (decltype(api.GetVersion))sym("ncclGetVersion");
-    api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllReduce && api.GetErrorString;
+    api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllReduce && api.ReduceScatter &&
+             api.AllGather && api.GetErrorString;
     if (!api.ok) api.error = "libnccl.so.2 lacks a required symbol";
   });
   return api;

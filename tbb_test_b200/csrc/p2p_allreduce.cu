@@ -4,9 +4,10 @@
 // ranks' gradient slabs, in rank order (so all ranks end with identical bits), and stores the
 // sum into every rank's slab. Ordering between ranks is by two flag exchanges per call,
 // "my input is ready" and "my stores are done"; flags carry a call counter (epoch) that only
-// grows, so they are never reset. Every wait is bounded: after WAIT_LIMIT_NS the kernel
+// grows, so they are never reset. Every wait is bounded: after P2pParams::wait_ns the kernel
 // records a status code and returns without signalling, so that the peers time out too and
-// every rank reports the failure.
+// every rank reports the failure; a launch that finds a failure already recorded returns at
+// once, so that the calls queued behind a failed one do not each wait out the limit.
 //
 // No TMA, no multicast: plain peer loads/stores issued per CTA.
 #include "common.cuh"
@@ -15,7 +16,6 @@ namespace b2 {
 
 namespace {
 
-constexpr unsigned long long WAIT_LIMIT_NS = 1000000000ull;  // 1 s
 constexpr int THREADS = 512;
 constexpr int MAX_CTAS = 32;
 
@@ -33,13 +33,14 @@ __device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) 
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// Spin until *flag has reached `epoch` (wrap-safe). False after WAIT_LIMIT_NS.
-__device__ bool wait_flag(const unsigned int* flag, unsigned int epoch, unsigned int* status, unsigned int code) {
+// Spin until *flag has reached `epoch` (wrap-safe). False after `limit_ns`.
+__device__ bool wait_flag(const unsigned int* flag, unsigned int epoch, unsigned long long limit_ns,
+                          unsigned int* status, unsigned int code) {
   if ((int)(ld_acquire_sys(flag) - epoch) >= 0) return true;
   const unsigned long long t0 = globaltimer_ns();
   unsigned int spins = 0;
   while ((int)(ld_acquire_sys(flag) - epoch) < 0) {
-    if ((++spins & 0x3F) == 0 && globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+    if ((++spins & 0x3F) == 0 && globaltimer_ns() - t0 > limit_ns) {
       atomicCAS(status, 0u, code);
       return false;
     }
@@ -55,10 +56,12 @@ __device__ void p2p_allreduce_body(const P2pParams& p, int cta, int nctas) {
   const int world = p.world, rank = p.rank;
   unsigned int* my_flags = p.flags[rank];
   if (t == 0) {
-    abort_s = 0;
+    // a wait of an earlier call already gave up: the call counters of the ranks no longer agree
+    abort_s = (*reinterpret_cast<volatile unsigned int*>(p.status) >= 100u) ? 1 : 0;
     last_s = 0;
   }
   __syncthreads();
+  if (abort_s) return;
 
   // ---- 1. my input is ready (it was written by earlier work of this stream); wait for the peers'
   if (t < world && t != rank) {
@@ -66,7 +69,7 @@ __device__ void p2p_allreduce_body(const P2pParams& p, int cta, int nctas) {
       __threadfence_system();
       st_release_sys(p.flags[t] + P2P_FLAG_ARRIVE + rank, p.epoch);
     }
-    if (!wait_flag(my_flags + P2P_FLAG_ARRIVE + t, p.epoch, p.status, 101u)) abort_s = 1;
+    if (!wait_flag(my_flags + P2P_FLAG_ARRIVE + t, p.epoch, p.wait_ns, p.status, 101u)) abort_s = 1;
   }
   __syncthreads();
   if (abort_s) return;  // no "done" signal: the peers give up as well and report it
@@ -120,7 +123,7 @@ __device__ void p2p_allreduce_body(const P2pParams& p, int cta, int nctas) {
   if (t < world && t != rank) {
     __threadfence_system();
     st_release_sys(p.flags[t] + P2P_FLAG_DONE + rank, p.epoch);
-    wait_flag(my_flags + P2P_FLAG_DONE + t, p.epoch, p.status, 102u);
+    wait_flag(my_flags + P2P_FLAG_DONE + t, p.epoch, p.wait_ns, p.status, 102u);
   }
 }
 

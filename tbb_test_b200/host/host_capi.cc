@@ -96,6 +96,15 @@ void b2h_plan_buckets(const size_t* layer_bytes, int nlayers, int world_size, in
                             bucket_high);
 }
 
+// The library's slab layout and slice ownership under the sharded update (csrc/bucket_plan.h).
+size_t b2h_slab_layout(const size_t* layer_elems, int nlayers, int world_size, size_t* offset, size_t* padded) {
+  return b2::plan_slab_layout(layer_elems, nlayers, world_size, offset, padded);
+}
+void b2h_bucket_slice(const size_t* offset, const size_t* padded, int low, int high, int world_size, int rank,
+                      size_t* out4) {
+  b2::plan_bucket_slice(offset, padded, low, high, world_size, rank, &out4[0], &out4[1], &out4[2], &out4[3]);
+}
+
 void b2h_ring_info(int nsock, int sid, int task, int* out3) {
   nsockets = nsock;
   get_my_ring_info(sid, task, &out3[0], &out3[1], &out3[2]);

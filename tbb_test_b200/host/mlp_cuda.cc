@@ -249,10 +249,10 @@ int main(int argc, char** argv) {
       t[FWD] = ph[l * B2_T_NUM + B2_T_FWD] * 1e-3;
       t[WGT_GRAD] = ph[l * B2_T_NUM + B2_T_WGT_GRAD] * 1e-3;
       t[BWD] = ph[l * B2_T_NUM + B2_T_BWD] * 1e-3;
-      // the collective stands where the reference has the reduce-scatter, the SGD
-      // kernel where it has the update + allgather
+      // the reduce-scatter (or allreduce) stands where the reference has its reduce-scatter, the
+      // SGD kernel plus the allgather of the weights where it has the update + allgather
       t[WGT_UPDATE_REDUCE_SCATTER] = ph[l * B2_T_NUM + B2_T_ALLREDUCE] * 1e-3;
-      t[WGT_UPDATE_ALLGATHER] = ph[l * B2_T_NUM + B2_T_WGT_UPDATE] * 1e-3;
+      t[WGT_UPDATE_ALLGATHER] = (ph[l * B2_T_NUM + B2_T_WGT_UPDATE] + ph[l * B2_T_NUM + B2_T_ALLGATHER]) * 1e-3;
       if (g == 0) {
         const double flops = 2.0 * batch_size * nfeatures[l] * nfeatures[l + 1] * NITER;  // mlp_omp.cc:492,584,675
         sum_flops[l][FWD] = sum_flops[l][WGT_GRAD] = sum_flops[l][BWD] = flops;

@@ -27,12 +27,12 @@ def nccl_unique_id():
     return bytes(buf)
 
 
-def p2p_emulate(bufs, device=0):
+def p2p_emulate(bufs, device=0, wait_ms=1000, lagging_rank=-1):
     """Sum of the equally long float32 arrays `bufs` (one per emulated rank) into each of them,
     by the peer-memory allreduce kernel with all ranks on one GPU."""
     arrs = [np.ascontiguousarray(b, dtype=np.float32) for b in bufs]
     ptrs = (_fp * len(arrs))(*[a.ctypes.data_as(_fp) for a in arrs])
-    rc = K.lib().b2_p2p_emulate(device, len(arrs), ptrs, arrs[0].size)
+    rc = K.lib().b2_p2p_emulate_opts(device, len(arrs), ptrs, arrs[0].size, wait_ms, lagging_rank)
     if rc != K.OK:
         raise K.B2Error(rc, K.lib().b2_last_error(None).decode())
     return arrs
@@ -41,7 +41,8 @@ def p2p_emulate(bufs, device=0):
 class MLP:
     def __init__(self, nfeatures, batch, *, rank=0, world_size=1, device=0, mode=K.MODE_BASELINE,
                  precision=K.PREC_FP32, grad_bf16=False, allreduce=True, overlap=True, input_grad=True,
-                 collect_timing=False, use_graph=False, force_simt=False, lr=0.01, nccl_id=None, comm_sms=-1, ar_bucket_mb=-1):
+                 collect_timing=False, use_graph=False, force_simt=False, lr=0.01, nccl_id=None, comm_sms=-1,
+                 ar_bucket_mb=-1, shard_update=-1):
         self.lib = K.lib()
         self.nf = [int(f) for f in nfeatures]
         self.L = len(self.nf) - 1
@@ -60,6 +61,7 @@ class MLP:
         cfg.lr = lr
         cfg.comm_sms = comm_sms
         cfg.ar_bucket_mb = ar_bucket_mb
+        cfg.shard_update = shard_update
         self._id = None
         if nccl_id is not None:
             self._id = C.create_string_buffer(bytes(nccl_id), K.NCCL_ID_BYTES)
@@ -192,10 +194,43 @@ class MLP:
                                         c.ctypes.data_as(_fp), n, epilogue, px, ldx))
         return c
 
+    def allreduce(self, dev_ptr, count, dtype=K.DTYPE_F32):
+        """In-place sum over all ranks of `count` elements at a device pointer of this GPU."""
+        self._ck(self.lib.b2_allreduce(self._h, dev_ptr, count, dtype))
+
     def allreduce_bench(self, count, dtype=K.DTYPE_F32, warmup=3, iters=10):
         ms, cs = C.c_double(), C.c_double()
         self._ck(self.lib.b2_allreduce_bench(self._h, count, dtype, warmup, iters, C.byref(ms), C.byref(cs)))
         return ms.value, cs.value
+
+    def collective_bench(self, kind, count, dtype=K.DTYPE_F32, warmup=3, iters=10):
+        """kind 0 allreduce, 1 reduce-scatter, 2 allgather; device ms per call."""
+        ms, cs = C.c_double(), C.c_double()
+        self._ck(self.lib.b2_collective_bench(self._h, kind, count, dtype, warmup, iters, C.byref(ms), C.byref(cs)))
+        return ms.value
+
+    def sgd_bench(self, nparams, grad_dtype=K.DTYPE_F32, with_bf16_copy=False, warmup=3, iters=20):
+        """(device ms per launch, algorithmic bytes per launch) of the SGD kernel on cold data."""
+        ms, by = C.c_double(), C.c_double()
+        self._ck(self.lib.b2_sgd_bench(self._h, nparams, grad_dtype, int(with_bf16_copy), warmup, iters, C.byref(ms),
+                                       C.byref(by)))
+        return ms.value, by.value
+
+    def set_timing(self, on):
+        self._ck(self.lib.b2_set_timing(self._h, int(on)))
+
+    def weights_fingerprint(self, l):
+        v = C.c_ulonglong()
+        self._ck(self.lib.b2_weights_fingerprint(self._h, l, C.byref(v)))
+        return v.value
+
+    def gemm_bench(self, form, m, n, k, precision, epilogue=K.EPI_NONE, out_dtype=K.DTYPE_F32, sms=0, warmup=3,
+                   iters=20):
+        """Device milliseconds per launch of one GEMM of the step alone (see b2_gemm_bench)."""
+        ms = C.c_double()
+        self._ck(self.lib.b2_gemm_bench(self._h, form, m, n, k, precision, epilogue, out_dtype, sms, warmup, iters,
+                                        C.byref(ms)))
+        return ms.value
 
     # -- peer-memory path for small gradient messages ------------------------
     def p2p_describe(self):
@@ -203,11 +238,13 @@ class MLP:
         self._ck(self.lib.b2_p2p_describe(self._h, buf))
         return bytes(buf)
 
-    def p2p_connect(self, descs, max_bytes):
+    def p2p_connect(self, descs, max_bytes, wait_ms=None):
         """descs: every rank's p2p_describe() bytes, in rank order."""
         blob = b"".join(descs)
         buf = C.create_string_buffer(blob, len(blob))
         self._ck(self.lib.b2_p2p_connect(self._h, buf, max_bytes))
+        if wait_ms is not None:
+            self._ck(self.lib.b2_p2p_set_wait_ms(self._h, wait_ms))
 
     # -- metrics ----------------------------------------------------------
     def timing(self):

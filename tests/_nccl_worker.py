@@ -35,16 +35,30 @@ def main():
     # 1. the reference's self-check (mlp_omp.cc:325-373) with one GPU per socket
     nrows, ncols = 256, 512
     w, g, e = O.kat(world, nrows, ncols)
-    dev = MLP([ncols, nrows], 8 * world, rank=rank, world_size=world, device=local, lr=1.0, nccl_id=fresh_id())
-    dev.upload_weights(0, w[rank])
-    dev.upload_weight_grad(0, g[rank])
-    dev.update_weight(0)
-    got = dev.weights(0)
-    assert np.array_equal(got, e), f"rank {rank}: allreduce+SGD known-answer test failed"
-    ms, checksum = dev.allreduce_bench(1 << 20, K.DTYPE_F32, 2, 5)
-    ref = sum(O.fill_uniform(1, 4096, r, -1.0, 1.0).astype(np.float64).sum() for r in range(world))
-    assert abs(checksum - ref) <= 1e-3, (checksum, ref)
-    dev.close()
+    # through both routes: reduce-scatter + SGD on the owned slice + allgather of the weights (the
+    # reference's own, mlp_omp.cc:90-146,240-258), and allreduce + SGD on every rank; fp32 operands
+    # and bf16 operands (where the allgather carries the bf16 copy and the download gathers the masters)
+    for shard in (1, 0):
+        for prec in (K.PREC_FP32, K.PREC_BF16):
+            dev = MLP([ncols, nrows], 8 * world, rank=rank, world_size=world, device=local, lr=1.0,
+                      nccl_id=fresh_id(), shard_update=shard, precision=prec)
+            dev.upload_weights(0, w[rank])
+            dev.upload_weight_grad(0, g[rank])
+            dev.update_weight(0)
+            got = dev.weights(0)
+            assert np.array_equal(got, e), f"rank {rank}: allreduce+SGD known-answer test failed (shard {shard})"
+            if shard == 1 and prec == K.PREC_FP32:
+                ms, checksum = dev.allreduce_bench(1 << 20, K.DTYPE_F32, 2, 5)
+                ref = sum(O.fill_uniform(1, 4096, r, -1.0, 1.0).astype(np.float64).sum() for r in range(world))
+                assert abs(checksum - ref) <= 1e-3, (checksum, ref)
+                # the same sum on a caller-owned device buffer (configuration 2 through the boundary)
+                buf = torch.from_numpy(O.fill_uniform(1, 70001, rank, -1.0, 1.0).ravel().copy()).cuda()
+                dev.allreduce(buf.data_ptr(), buf.numel(), K.DTYPE_F32)
+                want = np.zeros(70001, np.float64)
+                for r in range(world):
+                    want += O.fill_uniform(1, 70001, r, -1.0, 1.0).ravel()
+                assert np.abs(buf.cpu().numpy() - want).max() <= 1e-5  # the reference's own bound, mlp_omp.cc:360
+            dev.close()
 
     # 1b. the same known-answer test and a few steps of the deep narrow shape through the
     # peer-memory path (gradient sums of up to 4 MiB bypass NCCL), against the NCCL path
@@ -69,7 +83,7 @@ def main():
         results = []
         for p2p in (False, True):
             dev = MLP(nf_s, batch_s, rank=rank, world_size=world, device=local, precision=K.PREC_FP32, lr=0.01,
-                      nccl_id=fresh_id(), ar_bucket_mb=0)
+                      nccl_id=fresh_id(), ar_bucket_mb=0, shard_update=0)
             if p2p:
                 connected(dev)
             for l in range(3):
@@ -93,10 +107,10 @@ def main():
     for prec, rounding, tol in ((K.PREC_FP32, O.ROUND_NONE, dict(state=2e-5, grad=2e-5)),
                                 (K.PREC_BF16, O.ROUND_BF16, dict(state=5e-3, grad=1e-1))):
         # two-stream schedule with the default gradient buckets, with one collective per layer,
-        # and the serial schedule
-        for overlap, bucket in ((True, -1), (True, 0), (False, -1)):
+        # and the serial schedule; sharded update (default) and allreduce + full update
+        for overlap, bucket, shard in ((True, -1, 1), (True, 0, 1), (False, -1, 1), (True, -1, 0), (False, 0, 0)):
             dev = MLP(nf, batch, rank=rank, world_size=world, device=local, precision=prec, lr=0.01,
-                      nccl_id=fresh_id(), overlap=overlap, ar_bucket_mb=bucket)
+                      nccl_id=fresh_id(), overlap=overlap, ar_bucket_mb=bucket, shard_update=shard)
             orc = O.Oracle(nf, batch, nranks=world, mode=O.MODE_BASELINE, rounding=rounding, lr=0.01)
             for l in range(3):
                 dev.upload_weights(l, ws[l])
@@ -112,7 +126,8 @@ def main():
             assert rel_fro(dev.activation(3), orc.activation(3)[b0:b1]) <= tol["state"]
             for l in range(3):
                 assert rel_fro(dev.weights(l) - ws[l], orc.weights(l) - ws[l]) <= max(tol["state"], 3e-2 if prec else 0), l
-                assert rel_fro(dev.weight_grad(l), orc.weight_grad(l)) <= tol["grad"], l  # summed over ranks
+                if shard == 0:  # summed over ranks (with the sharded update no rank holds the whole sum)
+                    assert rel_fro(dev.weight_grad(l), orc.weight_grad(l)) <= tol["grad"], l
             loss = torch.tensor([dev.loss()], dtype=torch.float64)
             dist.all_reduce(loss)
             assert abs(loss.item() - orc.loss()) <= 2e-3 * abs(orc.loss())

@@ -30,6 +30,7 @@ def test_config_defaults_and_struct_size(native):
     assert K.lib().b2_config_default(C.byref(cfg)) == K.OK
     assert (cfg.world_size, cfg.mode, cfg.precision) == (1, K.MODE_BASELINE, K.PREC_FP32)
     assert (cfg.allreduce, cfg.overlap, cfg.input_grad, cfg.comm_sms) == (1, 1, 1, -1)
+    assert (cfg.ar_bucket_mb, cfg.shard_update) == (-1, -1)
     assert abs(cfg.lr - 0.01) < 1e-9
     assert K.lib().b2_version().startswith(b"b200mlp")
 

@@ -20,10 +20,15 @@ def torchrun(nproc, script_args, port, timeout=300):
                           timeout=timeout)
 
 
-@pytest.mark.parametrize("world,batch", [(2, 50), (3, 50)])
-def test_sharded_ranks_reproduce_the_single_job(native, oracle, tmp_path, world, batch):
+@pytest.mark.parametrize("world,batch,route", [(2, 50, "allreduce"), (3, 50, "allreduce"), (2, 50, "shard"),
+                                               (3, 50, "shard")])
+def test_sharded_ranks_reproduce_the_single_job(native, oracle, tmp_path, world, batch, route):
+    """Batch shards per rank, gradients summed over ranks: by allreduce + SGD everywhere, or by
+    the reference's route (mlp_omp.cc:90-146,240-258) on the library's slab layout - reduce-scatter
+    per bucket, SGD on the owned slice, allgather of the weights."""
     out = str(tmp_path / "w.npz")
-    r = torchrun(world, [os.path.join(ROOT, "tests", "_gloo_worker.py"), out, str(batch)], 29731 + world)
+    r = torchrun(world, [os.path.join(ROOT, "tests", "_gloo_worker.py"), out, str(batch), route],
+                 29731 + world + (10 if route == "shard" else 0))
     assert r.returncode == 0, r.stdout[-2000:]
     got = np.load(out)
     nf = [48, 64, 32]

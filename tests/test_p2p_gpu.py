@@ -1,15 +1,12 @@
 """Peer-memory allreduce for small gradient messages, with all ranks emulated on one GPU
 (one cooperative launch; the multi-GPU form of the same kernel is covered by
 tests/test_multigpu_gpu.py)."""
-import os
+import time
 
 import numpy as np
 import pytest
 
-pytestmark = [pytest.mark.gpu,
-              pytest.mark.skipif(os.environ.get("B2_TEST_P2P") != "1",
-                                 reason="the peer-memory allreduce kernel is not yet confirmed on a GPU: "
-                                        "set B2_TEST_P2P=1 to run it")]
+pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
@@ -38,3 +35,25 @@ def test_emulated_ranks_agree_bit_for_bit_on_reals(native, oracle):
     got = p2p_emulate([b.copy() for b in bufs])
     for r in range(world):
         assert np.array_equal(got[r], want), r
+
+
+@pytest.mark.parametrize("world,lagging", [(2, 1), (4, 0), (8, 5)])
+def test_a_rank_that_never_arrives_makes_every_wait_run_out(native, world, lagging):
+    """The reference's flag waits spin without a limit (mlp_omp.cc:120-121,267-268). Here a
+    rank that is one call behind never satisfies the others' waits: each wait gives up after
+    the limit, the kernel returns, and the host gets B2_ERR_TIMEOUT instead of a hang. The
+    failure is made on the host (a call counter one behind); the GPU stays usable."""
+    from tbb_test_b200 import _capi as K
+    from tbb_test_b200.mlp import p2p_emulate
+    count = 4096
+    bufs = [np.full(count, float(r + 1), np.float32) for r in range(world)]
+    t0 = time.time()
+    with pytest.raises(K.B2Error) as e:
+        p2p_emulate([b.copy() for b in bufs], wait_ms=50, lagging_rank=lagging)
+    assert e.value.code == K.ERR_TIMEOUT
+    assert time.time() - t0 < 5.0
+    # the device and the kernel are still good for the next call
+    got = p2p_emulate([b.copy() for b in bufs], wait_ms=50)
+    want = np.full(count, float(world * (world + 1) // 2), np.float32)
+    for r in range(world):
+        assert np.array_equal(got[r], want)
