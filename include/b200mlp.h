@@ -50,8 +50,13 @@ typedef enum {
 typedef enum {
   B2_PREC_FP32 = 0, /* fp32 operands, CUDA-core FMA (parity mode) */
   B2_PREC_TF32 = 1, /* fp32 storage, tcgen05 kind::tf32 */
-  B2_PREC_BF16 = 2  /* bf16 operands (activations, gradients, a bf16 weight copy),
+  B2_PREC_BF16 = 2, /* bf16 operands (activations, gradients, a bf16 weight copy),
                        tcgen05 kind::f16 */
+  B2_PREC_FP32_TC = 3 /* fp32 storage and fp32-class results on the tensor cores: every operand x
+                       is kept with its low-order twin x - tf32(x), and each k-step issues three
+                       kind::tf32 MMAs (A*B + A*B_lo + A_lo*B) into the same fp32 accumulator;
+                       same tolerance class as B2_PREC_FP32 (the reference's sgemm), about a
+                       third of the TF32 rate */
 } b2_precision;
 
 typedef enum { B2_DTYPE_F32 = 0, B2_DTYPE_BF16 = 1 } b2_dtype;
@@ -196,7 +201,8 @@ int b2_sgemm_host(b2_handle* h, int precision, int transa, int transb, int m, in
                   const float* a, size_t lda, const float* b, size_t ldb, float* c, size_t ldc,
                   int epilogue, const float* aux, size_t ldaux);
 /* Same on fp32 DEVICE pointers of this handle's GPU, alpha/beta like cblas
- * (FP32 precision: any alpha/beta; TF32: beta must be 0). Asynchronous on the
+ * (FP32 precision: any alpha/beta; TF32: beta must be 0; FP32_TC is served by
+ * b2_sgemm_host only, which has room for the operand twins). Asynchronous on the
  * handle's main stream; b2_sync() waits. */
 int b2_sgemm(b2_handle* h, int precision, int transa, int transb, int m, int n, int k, float alpha,
              const float* a, size_t lda, const float* b, size_t ldb, float beta, float* c,
@@ -211,8 +217,12 @@ int b2_sync(b2_handle* h);
  * calls no cudaMalloc/cudaFree: the bf16 operand copies and the kernel's status word
  * live in a fixed __device__ array of 16 MiB + 256 bytes that every GPU loading the
  * library holds until the process exits. Limits: op(A) and op(B) may each hold at most
- * B2_NOALLOC_MAX_OPERAND_ELEMS elements (larger ones return B2_ERR_UNSUPPORTED), and
- * pointers / leading dimensions must be 16-byte aligned. The array is shared by all
+ * B2_NOALLOC_MAX_OPERAND_ELEMS elements. `a` and `b` need no alignment (they are repacked
+ * into the scratch), but the packed copies must be addressable by TMA: the number of
+ * COLUMNS of each matrix as stored (k for a non-transposed A, m for a transposed one; n for
+ * a non-transposed B, k for a transposed one) must be a multiple of 8, `c` must be 16-byte
+ * aligned with ldc a multiple of 4, and n at least 16. A call outside these limits returns
+ * B2_ERR_UNSUPPORTED with the reason in b2_noalloc_last_error(). The array is shared by all
  * calls and keeps the previous call's contents: calls whose GPU work overlaps race.
  * The first call on a device looks up the array's address and should be made outside
  * stream capture. `stream` is a cudaStream_t (NULL = default stream); the call returns
@@ -326,6 +336,15 @@ int b2_reset_timing(b2_handle* h);
  * stream, 2 side stream). Same idea as the reference's COLLECT_TRACE dump (mlp_tbb.cc:82-108,
  * 1378-1392), with GPUs for sockets and streams for threads. */
 int b2_write_trace(b2_handle* h, const char* path);
+
+/* Which kernel serves the GEMM sites of the step (three per layer, plus the second input slot's):
+ * in the tensor-core precisions a site whose shape or alignment the tensor-core kernel cannot
+ * address (a leading dimension that is not a multiple of 16 bytes, fewer than 16 output columns,
+ * such as the 1-wide tail layer of the reference's topology, mlp_bench_common.h:26) falls to the
+ * CUDA-core kernel, about 30 times slower. The counts and the reason given for the first such
+ * site make that visible; with B2_VERBOSE set in the environment it is also printed once. */
+int b2_site_report(const b2_handle* h, int* tensor_core_sites, int* cuda_core_sites, char* first_reason,
+                   size_t reason_len);
 
 /* Number of kernels of this library launched on the handle since creation, and
  * how many of them were tensor-core (tcgen05) GEMMs. */

@@ -12,7 +12,7 @@ LIB_PATH = os.path.join(HERE, "csrc", "libb200mlp.so")
 
 OK, ERR_INVALID, ERR_CUDA, ERR_NCCL, ERR_UNSUPPORTED, ERR_TIMEOUT, ERR_STATE = 0, -1, -2, -3, -4, -5, -6
 MODE_REF, MODE_BASELINE = 0, 1
-PREC_FP32, PREC_TF32, PREC_BF16 = 0, 1, 2
+PREC_FP32, PREC_TF32, PREC_BF16, PREC_FP32_TC = 0, 1, 2, 3
 DTYPE_F32, DTYPE_BF16 = 0, 1
 EPI_NONE, EPI_RELU, EPI_MASK = 0, 1, 2
 T_FWD, T_WGT_GRAD, T_BWD, T_WGT_UPDATE, T_ALLREDUCE, T_ALLGATHER, T_NUM = 0, 1, 2, 3, 4, 5, 6
@@ -87,6 +87,7 @@ SYMBOLS = {
     "b2_get_gemm_busy_ms": (C.c_int, [_H, _dp]),
     "b2_reset_timing": (C.c_int, [_H]),
     "b2_write_trace": (C.c_int, [_H, C.c_char_p]),
+    "b2_site_report": (C.c_int, [_H, C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_char_p, C.c_size_t]),
     "b2_launch_counts": (C.c_int, [_H, C.POINTER(C.c_longlong), C.POINTER(C.c_longlong)]),
 }
 

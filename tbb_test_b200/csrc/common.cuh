@@ -39,6 +39,13 @@ struct GemmDesc {
   // workspace must not overlap on the GPU.
   float* ws;
   unsigned int* ws_flags;
+  // fp32-class tensor-core mode (in_type T_F32 only): low-order twins x - tf32(x) of both
+  // operands (same shapes and strides as A and B). With both set the kernel issues three tf32
+  // MMAs per k-step (A*B + A*B_lo + A_lo*B), which restores fp32-class accuracy. C_lo (same
+  // shape and ldc as C, fp32) receives the twin of the result for the GEMM that reads C next.
+  const void* A_lo;
+  const void* B_lo;
+  void* C_lo;
 };
 constexpr size_t TC_WS_SLOT_BYTES = 2 * 128 * 256 * sizeof(float);
 
@@ -89,12 +96,14 @@ cudaError_t convert_bf16_to_f32(const __nv_bfloat16* src, float* dst, size_t n, 
 // dz = y (ref) or (y - t) * inv_batch (baseline); loss += 0.5 * sum(d^2) * loss_scale
 cudaError_t loss_grad_launch(const float* y, const float* target, void* dz, int dz_type, size_t n,
                              int baseline, float inv_batch, double loss_scale, double* loss,
-                             cudaStream_t s);
-// w = fma(-lr, g, w); optional bf16 copy of the new weights
+                             cudaStream_t s, float* dz_lo = nullptr);
+// w = fma(-lr, g, w); optional bf16 copy of the new weights, optional low-order twin w - tf32(w)
 cudaError_t sgd_launch(float* w, const void* g, int g_type, __nv_bfloat16* w_bf16, size_t n, float lr,
-                       int sm_count, cudaStream_t s);
+                       int sm_count, cudaStream_t s, float* w_lo = nullptr);
 // *out += sum of the 32-bit words of buf modulo 2^64 (out must be zeroed by the caller)
 cudaError_t fingerprint_launch(const void* buf, size_t bytes, unsigned long long* out, cudaStream_t s);
+// dst = src - tf32(src): the part of an fp32 value the tensor core drops when it reads it as tf32
+cudaError_t split_lo_launch(const float* src, float* dst, size_t n, cudaStream_t s);
 cudaError_t fill_uniform_launch(void* buf, int type, size_t n, uint64_t seed, float lo, float hi,
                                 cudaStream_t s);
 

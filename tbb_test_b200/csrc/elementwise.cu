@@ -19,10 +19,14 @@ __device__ __forceinline__ uint64_t mix64(uint64_t z) {
 //   w = fma(-alpha, g, w)
 // Algorithmic traffic per parameter: read w (4) + read g (4 or 2) + write w (4)
 // (+ write the bf16 operand copy (2) in BF16 precision).
-template <bool G_BF16, bool W16>
+__device__ __forceinline__ float tf32_lo(float v) {  // v - tf32(v): what a tf32 read of v drops (exact)
+  return v - __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
+}
+
+template <bool G_BF16, bool W16, bool W_LO>
 __global__ void __launch_bounds__(256) sgd_kernel(float* __restrict__ w, const void* __restrict__ gv,
-                                                  __nv_bfloat16* __restrict__ w16, size_t n,
-                                                  float neg_lr) {
+                                                  __nv_bfloat16* __restrict__ w16, float* __restrict__ w_lo,
+                                                  size_t n, float neg_lr) {
   const size_t nvec = n / 4;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   float4* w4 = reinterpret_cast<float4*>(w);
@@ -51,6 +55,8 @@ __global__ void __launch_bounds__(256) sgd_kernel(float* __restrict__ w, const v
       o.y = *reinterpret_cast<uint32_t*>(&b);
       reinterpret_cast<uint2*>(w16)[i] = o;
     }
+    if (W_LO)
+      reinterpret_cast<float4*>(w_lo)[i] = make_float4(tf32_lo(wv.x), tf32_lo(wv.y), tf32_lo(wv.z), tf32_lo(wv.w));
   }
   // tail (n % 4 elements)
   for (size_t i = nvec * 4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
@@ -59,6 +65,7 @@ __global__ void __launch_bounds__(256) sgd_kernel(float* __restrict__ w, const v
     float v = fmaf(neg_lr, g, w[i]);
     w[i] = v;
     if (W16) w16[i] = __float2bfloat16_rn(v);
+    if (W_LO) w_lo[i] = tf32_lo(v);
   }
 }
 
@@ -68,8 +75,8 @@ __global__ void __launch_bounds__(256) sgd_kernel(float* __restrict__ w, const v
 template <typename TO>
 __global__ void __launch_bounds__(256) loss_grad_kernel(const float* __restrict__ y,
                                                         const float* __restrict__ t,
-                                                        TO* __restrict__ dz, size_t n, int baseline,
-                                                        float inv_batch, double loss_scale,
+                                                        TO* __restrict__ dz, float* __restrict__ dz_lo, size_t n,
+                                                        int baseline, float inv_batch, double loss_scale,
                                                         double* __restrict__ loss) {
   // fp32 partial sums per thread (a few hundred terms each), double from the block level up
   float local = 0.f;
@@ -86,6 +93,7 @@ __global__ void __launch_bounds__(256) loss_grad_kernel(const float* __restrict_
     local += 0.5f * (d.x * d.x + d.y * d.y + d.z * d.z + d.w * d.w);
     if (sizeof(TO) == 4) {
       reinterpret_cast<float4*>(dz)[i] = g;
+      if (dz_lo) reinterpret_cast<float4*>(dz_lo)[i] = make_float4(tf32_lo(g.x), tf32_lo(g.y), tf32_lo(g.z), tf32_lo(g.w));
     } else {
       __nv_bfloat162 a = __floats2bfloat162_rn(g.x, g.y);
       __nv_bfloat162 b = __floats2bfloat162_rn(g.z, g.w);
@@ -103,8 +111,12 @@ __global__ void __launch_bounds__(256) loss_grad_kernel(const float* __restrict_
       g = d * inv_batch;
     }
     local += 0.5f * d * d;
-    if (sizeof(TO) == 4) reinterpret_cast<float*>(dz)[i] = g;
-    else reinterpret_cast<__nv_bfloat16*>(dz)[i] = __float2bfloat16_rn(g);
+    if (sizeof(TO) == 4) {
+      reinterpret_cast<float*>(dz)[i] = g;
+      if (dz_lo) dz_lo[i] = tf32_lo(g);
+    } else {
+      reinterpret_cast<__nv_bfloat16*>(dz)[i] = __float2bfloat16_rn(g);
+    }
   }
   __shared__ double red[256];
   red[threadIdx.x] = (double)local;
@@ -131,6 +143,11 @@ __global__ void __launch_bounds__(256) f32_to_bf16_kernel(const float* __restric
   }
   for (size_t i = nvec * 4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
     dst[i] = __float2bfloat16_rn(src[i]);
+}
+
+__global__ void __launch_bounds__(256) split_lo_kernel(const float* __restrict__ src, float* __restrict__ dst, size_t n) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) dst[i] = tf32_lo(src[i]);
 }
 
 __global__ void __launch_bounds__(256) bf16_to_f32_kernel(const __nv_bfloat16* __restrict__ src,
@@ -194,31 +211,39 @@ int device_sms() {
 }  // namespace
 
 cudaError_t sgd_launch(float* w, const void* g, int g_type, __nv_bfloat16* w16, size_t n, float lr,
-                       int sm_count, cudaStream_t s) {
+                       int sm_count, cudaStream_t s, float* w_lo) {
   if (n == 0) return cudaSuccess;
   // 8 resident CTAs of 256 threads per SM keep enough 16-byte loads in flight
   int grid = grid_for(n / 4 + 1, sm_count, 8);
   float neg = -lr;
-  if (g_type == T_BF16) {
-    if (w16) sgd_kernel<true, true><<<grid, 256, 0, s>>>(w, g, w16, n, neg);
-    else sgd_kernel<true, false><<<grid, 256, 0, s>>>(w, g, w16, n, neg);
+  if (w_lo) {
+    sgd_kernel<false, false, true><<<grid, 256, 0, s>>>(w, g, nullptr, w_lo, n, neg);
+  } else if (g_type == T_BF16) {
+    if (w16) sgd_kernel<true, true, false><<<grid, 256, 0, s>>>(w, g, w16, nullptr, n, neg);
+    else sgd_kernel<true, false, false><<<grid, 256, 0, s>>>(w, g, w16, nullptr, n, neg);
   } else {
-    if (w16) sgd_kernel<false, true><<<grid, 256, 0, s>>>(w, g, w16, n, neg);
-    else sgd_kernel<false, false><<<grid, 256, 0, s>>>(w, g, w16, n, neg);
+    if (w16) sgd_kernel<false, true, false><<<grid, 256, 0, s>>>(w, g, w16, nullptr, n, neg);
+    else sgd_kernel<false, false, false><<<grid, 256, 0, s>>>(w, g, w16, nullptr, n, neg);
   }
+  return cudaGetLastError();
+}
+
+cudaError_t split_lo_launch(const float* src, float* dst, size_t n, cudaStream_t s) {
+  if (n == 0) return cudaSuccess;
+  split_lo_kernel<<<grid_for(n, device_sms(), 8), 256, 0, s>>>(src, dst, n);
   return cudaGetLastError();
 }
 
 cudaError_t loss_grad_launch(const float* y, const float* target, void* dz, int dz_type, size_t n,
                              int baseline, float inv_batch, double loss_scale, double* loss,
-                             cudaStream_t s) {
+                             cudaStream_t s, float* dz_lo) {
   if (n == 0) return cudaSuccess;
   int grid = grid_for(n / 4 + 1, device_sms(), 8);
   if (dz_type == T_BF16)
-    loss_grad_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(y, target, (__nv_bfloat16*)dz, n, baseline,
+    loss_grad_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(y, target, (__nv_bfloat16*)dz, nullptr, n, baseline,
                                                          inv_batch, loss_scale, loss);
   else
-    loss_grad_kernel<float><<<grid, 256, 0, s>>>(y, target, (float*)dz, n, baseline, inv_batch,
+    loss_grad_kernel<float><<<grid, 256, 0, s>>>(y, target, (float*)dz, dz_lo, n, baseline, inv_batch,
                                                  loss_scale, loss);
   return cudaGetLastError();
 }

@@ -66,6 +66,13 @@ struct b2_handle {
   __nv_bfloat16* w16_slab = nullptr;
   std::vector<float*> w;             // w_slab + dw_off[l]
   std::vector<__nv_bfloat16*> w16;   // w16_slab + dw_off[l]
+  // fp32-class tensor-core mode (B2_PREC_FP32_TC): low-order twins x - tf32(x) of every GEMM
+  // operand, produced where the operand itself is produced (uploads, GEMM epilogues, the
+  // output-gradient kernel, SGD)
+  bool x3 = false;
+  float* w_lo_slab = nullptr;
+  std::vector<float*> w_lo, act_lo, dz_lo;
+  float* act0_alt_lo = nullptr;
   bool shard = false;          // reduce-scatter + owned-slice SGD + allgather instead of allreduce + full SGD
   bool masters_stale = false;  // BF16 precision with shard: ranks hold current fp32 masters only for their slices
   std::vector<size_t> dw_pad;  // padded element count of layer l in the slabs (multiple of 128 * world)
@@ -132,6 +139,8 @@ struct b2_handle {
   double step_ms = 0;
   long long steps = 0, launches = 0, tc_launches = 0;
   cudaGraphExec_t graph_exec = nullptr;
+  int tensor_core_sites = 0, cuda_core_sites = 0;  // GEMM sites of the step by the kernel that serves them
+  std::string cuda_core_reason;                    // why the first refused site was refused
   std::string err;
 };
 
@@ -180,9 +189,22 @@ int make_site(b2_handle* h, Site& s, bool want_tc, int sms = 0) {
   s.active = s.d.M > 0 && s.d.N > 0 && s.d.K > 0;
   s.plan = nullptr;
   if (!s.active || !want_tc) return B2_OK;
-  char why[128];
+  char why[128] = "";
   s.plan = gemm_tc_plan_create(s.d, sms > 0 ? sms : h->gemm_sms, why, sizeof why);
-  return B2_OK;  // a refused plan silently means the CUDA-core kernel serves this site
+  if (!s.plan) {
+    // the CUDA-core kernel serves this site (about 30 x slower): counted, the first reason kept
+    // for b2_site_report, and announced once per handle when B2_VERBOSE is set
+    if (h->cuda_core_sites++ == 0) {
+      char buf[256];
+      snprintf(buf, sizeof buf, "GEMM %d x %d x %d: %s", s.d.M, s.d.N, s.d.K, why);
+      h->cuda_core_reason = buf;
+      if (getenv("B2_VERBOSE"))
+        fprintf(stderr, "b200mlp: rank %d: tensor-core kernel refused, CUDA-core kernel used: %s\n", h->cfg.rank, buf);
+    }
+  } else {
+    ++h->tensor_core_sites;
+  }
+  return B2_OK;
 }
 
 int run_site(b2_handle* h, const Site& s, cudaStream_t st) {
@@ -193,6 +215,10 @@ int run_site(b2_handle* h, const Site& s, cudaStream_t st) {
     CK(h, gemm_tc_launch(s.plan, st, h->status_dev));
   } else {
     CK(h, gemm_simt_launch(s.d, st));
+    if (s.d.C_lo) {  // fp32-class mode: the CUDA-core kernel served this site, so its result's twin is made here
+      CK(h, split_lo_launch(static_cast<const float*>(s.d.C), static_cast<float*>(s.d.C_lo), (size_t)s.d.M * s.d.N, st));
+      ++h->launches;
+    }
   }
   return B2_OK;
 }
@@ -304,6 +330,11 @@ int build_sites(b2_handle* h) {
     f.epilogue = (baseline && l < L - 1) ? EPI_RELU : EPI_NONE;
     f.in_type = h->op_type;
     f.out_type = (l == L - 1) ? T_F32 : h->op_type;
+    if (h->x3) {
+      f.A_lo = h->act_lo[l];
+      f.B_lo = h->w_lo[l];
+      f.C_lo = (l == L - 1) ? nullptr : h->act_lo[l + 1];
+    }
     h->fwd[l].d = f;
     make_site(h, h->fwd[l], tc);
     // weight gradient: dW[l] = dZ[l]^T * A[l] over this rank's rows (mlp_omp.cc:565-580)
@@ -316,6 +347,10 @@ int build_sites(b2_handle* h) {
     g.epilogue = EPI_NONE;
     g.in_type = h->op_type;
     g.out_type = h->grad_type;
+    if (h->x3) {
+      g.A_lo = h->dz_lo[l];
+      g.B_lo = h->act_lo[l];
+    }
     h->wgrad[l].d = g;
     make_site(h, h->wgrad[l], tc, wg_sms);
     // input gradient: dA[l] = dZ[l] * W[l] (mlp_omp.cc:655-671), masked by ReLU'(A[l])
@@ -330,15 +365,22 @@ int build_sites(b2_handle* h) {
     b.aux = h->act[l]; b.ldaux = fi;
     b.in_type = h->op_type;
     b.out_type = h->op_type;
+    if (h->x3) {
+      b.A_lo = h->dz_lo[l];
+      b.B_lo = h->w_lo[l];
+      b.C_lo = (l == 0) ? nullptr : h->dz_lo[l - 1];
+    }
     h->dgrad[l].d = b;
     make_site(h, h->dgrad[l], tc, dg_sms);
     if (l == 0 && !h->cfg.input_grad) h->dgrad[l].active = false;
     if (l == 0) {  // layer 0 reads the network input: one more pair of sites for the second slot
       h->fwd0_alt.d = f;
       h->fwd0_alt.d.A = h->act0_alt;
+      if (h->x3) h->fwd0_alt.d.A_lo = h->act0_alt_lo;
       make_site(h, h->fwd0_alt, tc);
       h->wgrad0_alt.d = g;
       h->wgrad0_alt.d.B = h->act0_alt;
+      if (h->x3) h->wgrad0_alt.d.B_lo = h->act0_alt_lo;
       make_site(h, h->wgrad0_alt, tc, wg_sms);
     }
   }
@@ -435,7 +477,8 @@ int bucket_shard_sgd(b2_handle* h, int low, int high, cudaStream_t st, bool time
   const size_t per = count / h->cfg.world_size, off = begin + (size_t)h->cfg.rank * per;
   if (timed) CK(h, cudaEventRecord(phase_ev(h, low, B2_T_WGT_UPDATE, 0), st));
   CK(h, sgd_launch(h->w_slab + off, static_cast<char*>(h->dw_slab) + off * esize(h->grad_type), h->grad_type,
-                   h->op_type == T_BF16 ? h->w16_slab + off : nullptr, per, h->cfg.lr, h->sms, st));
+                   h->op_type == T_BF16 ? h->w16_slab + off : nullptr, per, h->cfg.lr, h->sms, st,
+                   h->x3 ? h->w_lo_slab + off : nullptr));
   ++h->launches;
   if (timed) CK(h, cudaEventRecord(phase_ev(h, low, B2_T_WGT_UPDATE, 1), st));
   if (h->op_type == T_BF16) h->masters_stale = true;
@@ -454,6 +497,10 @@ int bucket_allgather(b2_handle* h, int low, int high, cudaStream_t st, bool time
   } else {
     float* base = h->w_slab + begin;
     NCK(h, nccl_api().AllGather(base + (size_t)h->cfg.rank * per, base, per, ncclFloat32, h->comm, st));
+    if (h->x3) {  // the twins of the slices that arrived from the other ranks
+      CK(h, split_lo_launch(base, h->w_lo_slab + begin, count, st));
+      ++h->launches;
+    }
   }
   if (timed) CK(h, cudaEventRecord(phase_ev(h, low, B2_T_ALLGATHER, 1), st));
   return B2_OK;
@@ -485,7 +532,7 @@ int layer_sgd(b2_handle* h, int l, cudaStream_t st, bool timed) {
   const size_t n = (size_t)h->nf[l + 1] * h->nf[l];
   if (timed) CK(h, cudaEventRecord(phase_ev(h, l, B2_T_WGT_UPDATE, 0), st));
   CK(h, sgd_launch(h->w[l], h->dw[l], h->grad_type, h->op_type == T_BF16 ? h->w16[l] : nullptr, n, h->cfg.lr,
-                   h->sms, st));
+                   h->sms, st, h->x3 ? h->w_lo[l] : nullptr));
   ++h->launches;
   if (timed) CK(h, cudaEventRecord(phase_ev(h, l, B2_T_WGT_UPDATE, 1), st));
   return B2_OK;
@@ -517,7 +564,8 @@ int enqueue_step(b2_handle* h, bool timed, int slot = 0) {
     const size_t n = (size_t)h->bl * h->nf[L];
     const bool baseline = h->cfg.mode == B2_MODE_BASELINE;
     CK(h, loss_grad_launch(h->y, target, h->dz[L - 1], h->op_type, n, baseline ? 1 : 0,
-                           1.0f / (float)h->cfg.batch, baseline ? 1.0 / (double)h->cfg.batch : 1.0, loss_acc, sm));
+                           1.0f / (float)h->cfg.batch, baseline ? 1.0 / (double)h->cfg.batch : 1.0, loss_acc, sm,
+                           h->x3 ? h->dz_lo[L - 1] : nullptr));
     if (n) ++h->launches;
     if (wg) CK(h, cudaEventRecord(h->ev_dz_last, sm));
   }
@@ -642,6 +690,10 @@ void free_all(b2_handle* h) {
   for (auto& s : h->dgrad) gemm_tc_plan_destroy(s.plan);
   cudaFree(h->w_slab);
   cudaFree(h->w16_slab);
+  cudaFree(h->w_lo_slab);
+  for (auto p : h->act_lo) cudaFree(p);
+  for (auto p : h->dz_lo) cudaFree(p);
+  cudaFree(h->act0_alt_lo);
   for (auto e : h->ev_shard)
     if (e) cudaEventDestroy(e);
   for (int r = 0; r < P2P_MAX_RANKS; ++r)
@@ -737,7 +789,7 @@ int b2_create(const b2_config* cfg, b2_handle** out) {
   if (cfg->batch < 1) return fail(nullptr, B2_ERR_INVALID, "batch must be positive");
   if (cfg->world_size < 1 || cfg->rank < 0 || cfg->rank >= cfg->world_size)
     return fail(nullptr, B2_ERR_INVALID, "rank %d outside world of %d", cfg->rank, cfg->world_size);
-  if (cfg->precision < B2_PREC_FP32 || cfg->precision > B2_PREC_BF16)
+  if (cfg->precision < B2_PREC_FP32 || cfg->precision > B2_PREC_FP32_TC)
     return fail(nullptr, B2_ERR_INVALID, "unknown precision %d", cfg->precision);
   if (cfg->mode != B2_MODE_REF && cfg->mode != B2_MODE_BASELINE)
     return fail(nullptr, B2_ERR_INVALID, "unknown mode %d", cfg->mode);
@@ -775,6 +827,7 @@ int b2_create(const b2_config* cfg, b2_handle** out) {
   h->bl = h->b1 - h->b0;
   h->op_type = cfg->precision == B2_PREC_BF16 ? T_BF16 : T_F32;
   h->grad_type = cfg->grad_bf16 ? T_BF16 : T_F32;
+  h->x3 = cfg->precision == B2_PREC_FP32_TC && !cfg->force_simt;
   int rc = B2_OK;
 #define TRY(x)            \
   do {                    \
@@ -834,11 +887,18 @@ int b2_create(const b2_config* cfg, b2_handle** out) {
   h->dz.assign(L, nullptr);
   h->act.assign(L + 1, nullptr);
   h->relu_bits.assign(L + 1, nullptr);
+  h->w_lo.assign(L, nullptr);
+  h->act_lo.assign(L + 1, nullptr);
+  h->dz_lo.assign(L, nullptr);
   size_t max_elems = 16;
   for (int l = 0; l < L; ++l) {
     const size_t nw = (size_t)h->nf[l + 1] * h->nf[l];
     TRY(dev_alloc(h, &h->dz[l], bl * h->nf[l + 1] * esize(h->op_type)));
     TRY(dev_alloc(h, &h->act[l], bl * h->nf[l] * esize(h->op_type)));
+    if (h->x3) {
+      TRY(dev_alloc(h, &h->dz_lo[l], bl * h->nf[l + 1] * 4));
+      TRY(dev_alloc(h, &h->act_lo[l], bl * h->nf[l] * 4));
+    }
     if (l > 0 && cfg->mode == B2_MODE_BASELINE && cfg->precision != B2_PREC_FP32 && !cfg->force_simt &&
         h->nf[l] % 32 == 0)
       TRY(dev_alloc(h, &h->relu_bits[l], bl * (size_t)(h->nf[l] / 32) * sizeof(uint32_t)));
@@ -858,9 +918,11 @@ int b2_create(const b2_config* cfg, b2_handle** out) {
     const size_t total = plan_slab_layout(layer_elems.data(), L, cfg->world_size, h->dw_off.data(), h->dw_pad.data());
     TRY(dev_alloc(h, &h->w_slab, total * 4));
     if (h->op_type == T_BF16) TRY(dev_alloc(h, &h->w16_slab, total * 2));
+    if (h->x3) TRY(dev_alloc(h, &h->w_lo_slab, total * 4));
     for (int l = 0; l < L; ++l) {
       h->w[l] = h->w_slab + h->dw_off[l];
       if (h->w16_slab) h->w16[l] = h->w16_slab + h->dw_off[l];
+      if (h->w_lo_slab) h->w_lo[l] = h->w_lo_slab + h->dw_off[l];
     }
     h->shard = cfg->world_size > 1 && cfg->allreduce && cfg->shard_update != 0;
     h->p2p_flags_off = (total * es + 255) / 256 * 256;
@@ -887,6 +949,7 @@ int b2_create(const b2_config* cfg, b2_handle** out) {
     TRY(dev_alloc(h, &h->stage, max_elems * 4));
   }
   TRY(dev_alloc(h, &h->act0_alt, bl * h->nf[0] * esize(h->op_type)));
+  if (h->x3) TRY(dev_alloc(h, &h->act0_alt_lo, bl * h->nf[0] * 4));
   TRY(dev_alloc(h, &h->target_alt, bl * h->nf[L] * 4));
   if (h->op_type == T_BF16)
     for (int i = 0; i < 2; ++i) TRY(dev_alloc(h, &h->xstage[i], bl * h->nf[0] * 4));
@@ -988,6 +1051,10 @@ int b2_upload_weights(b2_handle* h, int l, const float* host, size_t ld) {
     CK(h, convert_f32_to_bf16(h->w[l], h->w16[l], (size_t)rows * cols, h->s_main));
     ++h->launches;
   }
+  if (h->x3) {
+    CK(h, split_lo_launch(h->w[l], h->w_lo[l], (size_t)rows * cols, h->s_main));
+    ++h->launches;
+  }
   CK(h, cudaStreamSynchronize(h->s_main));
   return B2_OK;
 }
@@ -1006,6 +1073,10 @@ int b2_upload_input(b2_handle* h, const float* host, size_t ld) {
   if (!host || ld < (size_t)h->nf[0]) return fail(h, B2_ERR_INVALID, "bad host matrix");
   int rc = upload_matrix(h, h->act[0], h->op_type, host + (size_t)h->b0 * ld, ld, h->bl, h->nf[0]);
   if (rc) return rc;
+  if (h->x3 && h->bl > 0) {
+    CK(h, split_lo_launch(static_cast<const float*>(h->act[0]), h->act_lo[0], (size_t)h->bl * h->nf[0], h->s_main));
+    ++h->launches;
+  }
   CK(h, cudaStreamSynchronize(h->s_main));
   return B2_OK;
 }
@@ -1222,6 +1293,10 @@ int b2_train_step_host(b2_handle* h, const float* x, size_t ldx, const float* t,
   // fwd(0) of this step must not start before the copy; the copy must not start
   // before the previous step stopped reading act[0] - both hold on the main stream.
   if ((rc = upload_matrix(h, h->act[0], h->op_type, x + (size_t)h->b0 * ldx, ldx, h->bl, h->nf[0]))) return rc;
+  if (h->x3 && h->bl > 0) {
+    CK(h, split_lo_launch(static_cast<const float*>(h->act[0]), h->act_lo[0], (size_t)h->bl * h->nf[0], h->s_main));
+    ++h->launches;
+  }
   if (t) {
     if (ldt < (size_t)h->nf[h->L]) return fail(h, B2_ERR_INVALID, "bad target matrix");
     if ((rc = upload_matrix(h, h->target, T_F32, t + (size_t)h->b0 * ldt, ldt, h->bl, h->nf[h->L]))) return rc;
@@ -1251,6 +1326,11 @@ int b2_train_step_host_async(b2_handle* h, const float* x, size_t ldx, const flo
                             cudaMemcpyHostToDevice, h->s_copy));
     if (h->op_type == T_BF16) {
       CK(h, convert_f32_to_bf16(h->xstage[slot], (__nv_bfloat16*)act0, (size_t)rows * f0, h->s_copy));
+      ++h->launches;
+    }
+    if (h->x3) {
+      CK(h, split_lo_launch(static_cast<const float*>(act0), slot ? h->act0_alt_lo : h->act_lo[0], (size_t)rows * f0,
+                            h->s_copy));
       ++h->launches;
     }
     if (t)
@@ -1656,7 +1736,7 @@ int b2_gemm_bench(b2_handle* h, int form, int m, int n, int k, int precision, in
   ENTER(h);
   if (form < 0 || form > 2 || m < 1 || n < 1 || k < 1 || iters < 1 || warmup < 0)
     return fail(h, B2_ERR_INVALID, "bad GEMM benchmark arguments");
-  if (precision != B2_PREC_TF32 && precision != B2_PREC_BF16 && precision != B2_PREC_FP32)
+  if (precision < B2_PREC_FP32 || precision > B2_PREC_FP32_TC)
     return fail(h, B2_ERR_INVALID, "unknown precision %d", precision);
   if (epilogue < EPI_NONE || epilogue > EPI_MASK) return fail(h, B2_ERR_INVALID, "bad epilogue");
   const int in_type = precision == B2_PREC_BF16 ? T_BF16 : T_F32;
@@ -1668,8 +1748,9 @@ int b2_gemm_bench(b2_handle* h, int form, int m, int n, int k, int precision, in
   int sets = (int)((size_t(384) << 20) / set_bytes) + 1;
   if (sets > 16) sets = 16;
   if (sets < 1) sets = 1;
-  struct Set { void *a, *b, *c, *x; TcPlan* plan; GemmDesc d; };
-  std::vector<Set> S(sets, Set{nullptr, nullptr, nullptr, nullptr, nullptr, GemmDesc{}});
+  struct Set { void *a, *b, *c, *x; float *a_lo, *b_lo, *c_lo; TcPlan* plan; GemmDesc d; };
+  std::vector<Set> S(sets, Set{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, GemmDesc{}});
+  const bool x3 = precision == B2_PREC_FP32_TC && !h->cfg.force_simt;
   int rc = B2_OK;
   const bool tc = precision != B2_PREC_FP32 && !h->cfg.force_simt;
   do {
@@ -1683,6 +1764,15 @@ int b2_gemm_bench(b2_handle* h, int form, int m, int n, int k, int precision, in
       }
       fill_uniform_launch(s.a, in_type, ea, 7 + 3 * i, -1.f, 1.f, h->s_main);
       fill_uniform_launch(s.b, in_type, eb, 8 + 3 * i, -1.f, 1.f, h->s_main);
+      if (x3) {
+        if (cudaMalloc((void**)&s.a_lo, ea * 4) != cudaSuccess || cudaMalloc((void**)&s.b_lo, eb * 4) != cudaSuccess ||
+            cudaMalloc((void**)&s.c_lo, ec * 4) != cudaSuccess) {
+          rc = fail(h, B2_ERR_CUDA, "cudaMalloc: %s", cudaGetErrorString(cudaGetLastError()));
+          break;
+        }
+        split_lo_launch(static_cast<const float*>(s.a), s.a_lo, ea, h->s_main);
+        split_lo_launch(static_cast<const float*>(s.b), s.b_lo, eb, h->s_main);
+      }
       if (s.x) fill_uniform_launch(s.x, in_type, ec, 9 + 3 * i, -1.f, 1.f, h->s_main);
       GemmDesc& d = s.d;
       d.M = m; d.N = n; d.K = k;
@@ -1699,6 +1789,8 @@ int b2_gemm_bench(b2_handle* h, int form, int m, int n, int k, int precision, in
       d.epilogue = epilogue;
       d.in_type = in_type; d.out_type = out_type;
       d.ws = nullptr; d.ws_flags = nullptr;
+      d.A_lo = s.a_lo; d.B_lo = s.b_lo;
+      d.C_lo = (x3 && form != 1) ? s.c_lo : nullptr;  // like the step: activations and gradients get a twin
       if (tc) {
         char why[128] = "";
         s.plan = gemm_tc_plan_create(d, sms > 0 && sms <= h->sms ? sms : h->sms, why, sizeof why);
@@ -1739,6 +1831,7 @@ int b2_gemm_bench(b2_handle* h, int form, int m, int n, int k, int precision, in
   for (auto& s : S) {
     gemm_tc_plan_destroy(s.plan);
     cudaFree(s.a); cudaFree(s.b); cudaFree(s.c); cudaFree(s.x);
+    cudaFree(s.a_lo); cudaFree(s.b_lo); cudaFree(s.c_lo);
   }
   return rc;
 }
@@ -1787,6 +1880,15 @@ int b2_reset_timing(b2_handle* h) {
   return B2_OK;
 }
 
+int b2_site_report(const b2_handle* h, int* tensor_core_sites, int* cuda_core_sites, char* first_reason,
+                   size_t reason_len) {
+  if (!h) return B2_ERR_INVALID;
+  if (tensor_core_sites) *tensor_core_sites = h->tensor_core_sites;
+  if (cuda_core_sites) *cuda_core_sites = h->cuda_core_sites;
+  if (first_reason && reason_len) snprintf(first_reason, reason_len, "%s", h->cuda_core_reason.c_str());
+  return B2_OK;
+}
+
 int b2_launch_counts(const b2_handle* h, long long* total, long long* tc) {
   if (!h) return B2_ERR_INVALID;
   if (total) *total = h->launches;
@@ -1824,6 +1926,8 @@ int b2_sgemm(b2_handle* h, int precision, int transa, int transb, int m, int n, 
              size_t lda, const float* b, size_t ldb, float beta, float* c, size_t ldc) {
   ENTER(h);
   if (precision == B2_PREC_BF16) return fail(h, B2_ERR_UNSUPPORTED, "b2_sgemm takes fp32 device operands");
+  if (precision == B2_PREC_FP32_TC)
+    return fail(h, B2_ERR_UNSUPPORTED, "b2_sgemm has no room for the operand twins of the fp32-class mode: b2_sgemm_host");
   if (m < 0 || n < 0 || k < 0 || !a || !b || !c) return fail(h, B2_ERR_INVALID, "bad GEMM arguments");
   GemmDesc d{};
   d.M = m; d.N = n; d.K = k;
@@ -1849,6 +1953,8 @@ int b2_sgemm_host(b2_handle* h, int precision, int transa, int transb, int m, in
   const int ar = transa ? k : m, ac = transa ? m : k;
   const int br = transb ? n : k, bc = transb ? k : n;
   void *da = nullptr, *db = nullptr, *dc = nullptr, *dx = nullptr;
+  float *da_lo = nullptr, *db_lo = nullptr;
+  const bool x3 = precision == B2_PREC_FP32_TC && !h->cfg.force_simt;
   float* stage = nullptr;
   size_t big = (size_t)ar * ac;
   if ((size_t)br * bc > big) big = (size_t)br * bc;
@@ -1873,6 +1979,12 @@ int b2_sgemm_host(b2_handle* h, int precision, int transa, int transb, int m, in
     if ((rc = put(&db, b, ldb, br, bc))) break;
     if (epilogue == EPI_MASK && (rc = put(&dx, aux, ldaux, m, n))) break;
     if (cudaMalloc(&dc, (size_t)m * n * esize(out_type)) != cudaSuccess) { rc = fail(h, B2_ERR_CUDA, "cudaMalloc"); break; }
+    if (x3) {
+      if (cudaMalloc((void**)&da_lo, (size_t)ar * ac * 4) != cudaSuccess ||
+          cudaMalloc((void**)&db_lo, (size_t)br * bc * 4) != cudaSuccess) { rc = fail(h, B2_ERR_CUDA, "cudaMalloc"); break; }
+      split_lo_launch(static_cast<const float*>(da), da_lo, (size_t)ar * ac, h->s_main);
+      split_lo_launch(static_cast<const float*>(db), db_lo, (size_t)br * bc, h->s_main);
+    }
     GemmDesc d{};
     d.M = m; d.N = n; d.K = k;
     d.A = da; d.sAm = transa ? 1 : ac; d.sAk = transa ? ac : 1;
@@ -1882,6 +1994,7 @@ int b2_sgemm_host(b2_handle* h, int precision, int transa, int transb, int m, in
     d.alpha = 1.f; d.beta = 0.f;
     d.epilogue = epilogue;
     d.in_type = in_type; d.out_type = out_type;
+    d.A_lo = da_lo; d.B_lo = db_lo;
     if ((rc = gemm_common(h, precision, d, h->s_main))) break;
     const void* src = dc;
     if (out_type == T_BF16) {
@@ -1900,6 +2013,7 @@ int b2_sgemm_host(b2_handle* h, int precision, int transa, int transb, int m, in
     rc = check_status(h);
   } while (0);
   cudaFree(da); cudaFree(db); cudaFree(dc); cudaFree(dx); cudaFree(stage);
+  cudaFree(da_lo); cudaFree(db_lo);
   return rc;
 }
 

@@ -33,6 +33,7 @@
 #include <cuda.h>
 
 #include <cmath>
+#include <mutex>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -99,6 +100,10 @@ struct TcParams {
   uint32_t* mask_out;
   const uint32_t* mask_in;
   long long ld_mask;  // words per row
+  // fp32-class mode (three tf32 MMAs per k-step on operands split into a high and a low part):
+  // x3 = the stage holds A, A_lo, B, B_lo; c_lo = the epilogue also writes the low-order twin
+  // of C (v - tf32(v)) for the GEMM that will read C as an operand
+  int x3, c_lo;
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -232,10 +237,38 @@ __device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
 // between two MMAs is what bounds the tensor pipe's duty cycle: the constant descriptor
 // fields are assembled once per kernel, and per MMA only the 14-bit start-address field
 // (address >> 4) is added in.
+template <bool TF32, bool PAIR>
+__device__ __forceinline__ void mma_issue(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  if (PAIR) {
+    if (TF32)
+      asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                   "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+                   ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+    else
+      asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                   "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                   ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+  } else {
+    if (TF32)
+      asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                   "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+                   ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+    else
+      asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                   "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                   ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+  }
+}
+// With alo16 / blo16 != 0 (fp32-class mode, tf32 only) the stage also holds the low-order
+// twins of both slabs, alo16 / blo16 sixteen-byte units behind the slabs themselves, and every
+// k-step issues three MMAs: A*B, A*B_lo and A_lo*B (the tensor core truncates fp32 operands
+// to tf32, so A and B stand for their own high parts; A_lo*B_lo, 2^-22 of the product, is dropped).
 template <int SUB_M, bool TF32, bool PAIR>
 __device__ __forceinline__ void issue_kblock(uint32_t tmem_d, uint64_t a_tmpl, uint64_t b_tmpl, uint32_t sa16,
                                              uint32_t sb16, uint32_t a_step16, uint32_t b_step16, uint32_t idesc,
-                                             uint32_t block_n, int sub, bool first_kblock) {
+                                             uint32_t block_n, int sub, bool first_kblock, uint32_t alo16 = 0,
+                                             uint32_t blo16 = 0) {
 #pragma unroll
   for (int ks = 0; ks < KSTEPS; ++ks) {
     const uint64_t bdesc = b_tmpl + (uint64_t)(sb16 + ks * b_step16);
@@ -245,24 +278,10 @@ __device__ __forceinline__ void issue_kblock(uint32_t tmem_d, uint64_t a_tmpl, u
       if (i < sub) {
         const uint64_t adesc = a_tmpl + (uint64_t)(sa16 + i * ((BLOCK_M * SLAB_BYTES) >> 4) + ks * a_step16);
         const uint32_t d = tmem_d + (uint32_t)i * block_n;
-        if (PAIR) {
-          if (TF32)
-            asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                         "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-                         ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-          else
-            asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                         "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                         ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-        } else {
-          if (TF32)
-            asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                         "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-                         ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-          else
-            asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                         ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+        mma_issue<TF32, PAIR>(d, adesc, bdesc, idesc, accumulate);
+        if (TF32 && !PAIR && SUB_M == 1 && alo16 != 0) {
+          mma_issue<TF32, PAIR>(d, adesc, bdesc + (uint64_t)blo16, idesc, 1u);
+          mma_issue<TF32, PAIR>(d, adesc + (uint64_t)alo16, bdesc, idesc, 1u);
         }
       }
     }
@@ -466,9 +485,9 @@ __device__ __forceinline__ uint32_t mask_from_values(const TcParams& p, int row,
 // once, right after the last chunk has been read out of TMEM. `buf` = this warp's chunk
 // buffers (EPI_BUFS x 4 KB, 1024-byte aligned), `buf_i` = the one to use next (kept between tiles).
 template <int EPI_BUFS, typename Release>
-__device__ __forceinline__ void epilogue_rows_tma(const TcParams& p, const CUtensorMap* tma_c, uint32_t taddr,
-                                                  int row0, int n0, uint8_t* buf, int& buf_i, int lane,
-                                                  Release release) {
+__device__ __forceinline__ void epilogue_rows_tma(const TcParams& p, const CUtensorMap* tma_c,
+                                                  const CUtensorMap* tma_c_lo, uint32_t taddr, int row0, int n0,
+                                                  uint8_t* buf, int& buf_i, int lane, Release release) {
   const int row = row0 + lane;
   const int chunk_cols = p.out_bf16 ? 64 : 32;  // 128 bytes of C per row and chunk
   const int nchunks = p.block_n / chunk_cols;
@@ -529,6 +548,29 @@ __device__ __forceinline__ void epilogue_rows_tma(const TcParams& p, const CUten
       bulk_commit();
     }
     buf_i = (buf_i + 1 == EPI_BUFS) ? 0 : buf_i + 1;
+    if (p.c_lo) {
+      // fp32-class mode: the low-order twin of the chunk, v - tf32(v) (exact), through the next buffer
+      if (lane == 0) bulk_wait_read<EPI_BUFS - 1>();
+      __syncwarp();
+      uint8_t* dst2 = buf + (size_t)buf_i * 4096 + (size_t)lane * 128;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        uint32_t lo[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float v = __uint_as_float(words[4 * j + t]);
+          lo[t] = __float_as_uint(v - __uint_as_float(words[4 * j + t] & 0xFFFFE000u));
+        }
+        *reinterpret_cast<uint4*>(dst2 + ((j ^ swz) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0 && row0 < p.M) {
+        tma_store_2d(tma_c_lo, buf + (size_t)buf_i * 4096, col0, row0);
+        bulk_commit();
+      }
+      buf_i = (buf_i + 1 == EPI_BUFS) ? 0 : buf_i + 1;
+    }
   }
 }
 
@@ -599,7 +641,9 @@ __device__ __forceinline__ void epilogue_bar_sync(int nthreads) {
 template <int SUB_M>
 __global__ void __launch_bounds__(SUB_M == 2 ? NUM_THREADS_SUB2 : NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-               const __grid_constant__ CUtensorMap tma_c, const __grid_constant__ TcParams p) {
+               const __grid_constant__ CUtensorMap tma_c, const __grid_constant__ CUtensorMap tma_a_lo,
+               const __grid_constant__ CUtensorMap tma_b_lo, const __grid_constant__ CUtensorMap tma_c_lo,
+               const __grid_constant__ TcParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[MAX_STAGES];
   __shared__ __align__(8) uint64_t empty_bar[MAX_STAGES];
@@ -609,7 +653,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   __shared__ int abort_s;
 
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  const uint32_t stage_bytes = p.a_stage_bytes + p.b_stage_bytes;
+  // stage layout: A [A_lo] B [B_lo] (the low-order twins only in the fp32-class mode)
+  const uint32_t lo_mul = p.x3 ? 2u : 1u;
+  const uint32_t stage_bytes = (p.a_stage_bytes + p.b_stage_bytes) * lo_mul;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort_flag = &abort_s;
 
@@ -656,26 +702,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         for (int kb = it.kb0; kb < it.kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, 1u)) { ok = false; break; }
           uint8_t* sa = smem + (size_t)stage * stage_bytes;
-          uint8_t* sb = sa + p.a_stage_bytes;
-          mbar_expect_tx(&full_bar[stage], a_bytes + p.b_stage_bytes);
+          uint8_t* sb = sa + p.a_stage_bytes * lo_mul;
+          mbar_expect_tx(&full_bar[stage], (a_bytes + p.b_stage_bytes) * lo_mul);
           const int k0 = kb * p.block_k;
-          if (p.a_mn) {
-            const int nbox = it.sub * p.a_boxes;  // a_boxes per 128 rows
-            for (int b = 0; b < nbox; ++b)
-              tma_load_2d(&tma_a, &full_bar[stage], sa + (size_t)b * p.a_box_bytes, it.m0 + b * p.a_box_mn, k0);
-          } else {
+          for (uint32_t part = 0; part < lo_mul; ++part) {  // the operands, then their low-order twins
+            const CUtensorMap* ma = part ? &tma_a_lo : &tma_a;
+            const CUtensorMap* mb = part ? &tma_b_lo : &tma_b;
+            uint8_t* da = sa + part * p.a_stage_bytes;
+            uint8_t* db = sb + part * p.b_stage_bytes;
+            if (p.a_mn) {
+              const int nbox = it.sub * p.a_boxes;  // a_boxes per 128 rows
+              for (int b = 0; b < nbox; ++b)
+                tma_load_2d(ma, &full_bar[stage], da + (size_t)b * p.a_box_bytes, it.m0 + b * p.a_box_mn, k0);
+            } else {
 #pragma unroll
-            for (int i = 0; i < SUB_M; ++i)
-              if (i < it.sub)
-                tma_load_2d(&tma_a, &full_bar[stage], sa + (size_t)i * (BLOCK_M * SLAB_BYTES), k0,
-                            it.m0 + i * BLOCK_M);
-          }
-          if (p.b_mn) {
-            for (int b = 0; b < p.b_boxes; ++b)
-              tma_load_2d(&tma_b, &full_bar[stage], sb + (size_t)b * p.b_box_bytes,
-                          it.n_blk * p.block_n + b * p.b_box_mn, k0);
-          } else {
-            tma_load_2d(&tma_b, &full_bar[stage], sb, k0, it.n_blk * p.block_n);
+              for (int i = 0; i < SUB_M; ++i)
+                if (i < it.sub)
+                  tma_load_2d(ma, &full_bar[stage], da + (size_t)i * (BLOCK_M * SLAB_BYTES), k0, it.m0 + i * BLOCK_M);
+            }
+            if (p.b_mn) {
+              for (int b = 0; b < p.b_boxes; ++b)
+                tma_load_2d(mb, &full_bar[stage], db + (size_t)b * p.b_box_bytes, it.n_blk * p.block_n + b * p.b_box_mn,
+                            k0);
+            } else {
+              tma_load_2d(mb, &full_bar[stage], db, k0, it.n_blk * p.block_n);
+            }
           }
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
@@ -700,6 +751,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       const uint32_t a_step16 = p.a_kstep >> 4, b_step16 = p.b_kstep >> 4, idesc = p.idesc;
       const uint32_t block_n = (uint32_t)p.block_n;
       const bool tf32 = p.kind_tf32 != 0;
+      const uint32_t alo16 = p.x3 ? a_stage16 : 0u, blo16 = p.x3 ? (p.b_stage_bytes >> 4) : 0u;
       WorkIter wi;
       Work it;
       work_begin(p, wi);
@@ -712,8 +764,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           tc_fence_after();
           const uint32_t sa16 = smem16 + (uint32_t)stage * stage16;
           if (tf32)
-            issue_kblock<SUB_M, true, false>(tmem_d, a_tmpl, b_tmpl, sa16, sa16 + a_stage16, a_step16, b_step16,
-                                             idesc, block_n, it.sub, kb == it.kb0);
+            issue_kblock<SUB_M, true, false>(tmem_d, a_tmpl, b_tmpl, sa16, sa16 + a_stage16 * lo_mul, a_step16, b_step16,
+                                             idesc, block_n, it.sub, kb == it.kb0, alo16, blo16);
           else
             issue_kblock<SUB_M, false, false>(tmem_d, a_tmpl, b_tmpl, sa16, sa16 + a_stage16, a_step16, b_step16,
                                               idesc, block_n, it.sub, kb == it.kb0);
@@ -747,7 +799,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         uint64_t* release_bar = &acc_empty_bar[acc];
         if (sub < it.sub) {
           epilogue_rows_tma<EPI_BUFS>(
-              p, &tma_c,
+              p, &tma_c, &tma_c_lo,
               tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * acc_cols + (uint32_t)(sub * p.block_n),
               it.m0 + sub * BLOCK_M + q * 32, n_blk * p.block_n, ebuf, ebuf_i, lane,
               [&]() { if (lane == 0) mbar_arrive(release_bar); });
@@ -992,7 +1044,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       tc_fence_after();
       if (p.tma_store) {
         const uint32_t release_addr = map_to_cta(smem_u32(&acc_empty_bar[acc]), 0);
-        epilogue_rows_tma<2>(p, &tma_c, tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * p.block_n),
+        epilogue_rows_tma<2>(p, &tma_c, &tma_c, tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * p.block_n),
                              it.m0 + (int)rank * BLOCK_M + q * 32, it.n_blk * p.block_n, ebuf, ebuf_i, lane,
                              [&]() { if (lane == 0) mbar_arrive_cluster(release_addr); });
         acc ^= 1;
@@ -1066,7 +1118,7 @@ bool make_map(CUtensorMap* map, const void* base, int elem_bytes, long long inne
 }  // namespace
 
 struct TcPlan {
-  CUtensorMap map_a, map_b, map_c;
+  CUtensorMap map_a, map_b, map_c, map_a_lo, map_b_lo, map_c_lo;
   TcParams p;
   int grid;
   size_t smem;
@@ -1081,6 +1133,10 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
   const int ob = g.out_type == T_BF16 ? 2 : 4;
   if (g.M <= 0 || g.N <= 0 || g.K <= 0) return fail("empty GEMM");
   if (g.beta != 0.f) return fail("beta != 0");
+  const bool x3 = g.A_lo != nullptr && g.B_lo != nullptr;
+  if ((g.A_lo != nullptr) != (g.B_lo != nullptr)) return fail("fp32-class mode needs the twins of both operands");
+  if (x3 && eb != 4) return fail("fp32-class mode is for fp32 operands");
+  if (g.C_lo && ob != 4) return fail("a result twin needs an fp32 result");
   const bool a_mn = (g.sAm == 1 && g.sAk != 1), b_mn = (g.sBn == 1 && g.sBk != 1);
   if (!a_mn && g.sAk != 1) return fail("A has no unit stride");
   if (!b_mn && g.sBk != 1) return fail("B has no unit stride");
@@ -1089,6 +1145,8 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
     return (reinterpret_cast<uintptr_t>(p) % 16 == 0) && ((ld * bytes) % 16 == 0);
   };
   if (!aligned(g.A, lda, eb) || !aligned(g.B, ldb, eb)) return fail("operand not 16-byte aligned");
+  if (x3 && (!aligned(g.A_lo, lda, eb) || !aligned(g.B_lo, ldb, eb))) return fail("operand twin not 16-byte aligned");
+  if (g.C_lo && !aligned(g.C_lo, g.ldc, ob)) return fail("result twin not 16-byte aligned");
   if (!aligned(g.C, g.ldc, ob)) return fail("output not 16-byte aligned");
   if (g.epilogue == EPI_MASK && !aligned(g.aux, g.ldaux, eb)) return fail("mask operand not 16-byte aligned");
   if (g.N < 16) return fail("N < 16");
@@ -1116,6 +1174,7 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
     for (int i = 0; i < 4; ++i) {
       const Cand& c = cands[i];
       if (c.bn / 2 >= g.N && c.bn > 64) continue;  // tile wider than twice the matrix
+      if (x3 && (c.sub_m == 2 || c.bn == 256)) continue;  // twice the shared memory per stage: 128 x 128 at most
       const long long T = tiles(c.sub_m * BLOCK_M, c.bn);
       double waves;
       if (c.sub_m == 2) {
@@ -1138,11 +1197,12 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
     const int v = atoi(fb);
     if (v == 64 || v == 128 || v == 256) { bn = v; p.block_n = v; if (v != 256) p.sub_m = 1; }
   }
+  if (x3 && (bn == 256 || p.sub_m == 2)) { bn = 128; p.block_n = 128; p.sub_m = 1; }
   // CTA pairs: a 256 x 256 tile per pair of SMs once there is a tile for every pair
   {
     const char* pe = getenv("B2_TC_PAIR");
     const bool want = pe ? (pe[0] == '1') : false;
-    p.pair = (want && bn == 256 && tiles(2 * BLOCK_M, bn) >= sm_count / 2) ? 1 : 0;
+    p.pair = (want && !x3 && bn == 256 && tiles(2 * BLOCK_M, bn) >= sm_count / 2) ? 1 : 0;
     if (p.pair) p.sub_m = 2;  // tile rows for the work decomposition: 128 per CTA of the pair
   }
   p.acc_stages = (p.sub_m == 2 && !p.pair) ? 1 : 2;
@@ -1174,7 +1234,7 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
     // as much as the idle part of the last wave they remove; it pays for long-K shapes only.
     const char* sk = getenv("B2_TC_STREAMK");
     const bool allow = sk ? (sk[0] == '1') : false;
-    p.streamk = (allow && !p.pair && g.ws && g.ws_flags && T % sm_count != 0 && p.total_units >= sm_count) ? 1 : 0;
+    p.streamk = (allow && !p.pair && !x3 && g.ws && g.ws_flags && T % sm_count != 0 && p.total_units >= sm_count) ? 1 : 0;
     p.ws = g.ws;
     p.ws_flags = g.ws_flags;
     if (p.streamk) {
@@ -1208,6 +1268,7 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
     p.a_layout = mn_layout;
     p.a_kstep = (KSTEP_BYTES / eb) * SLAB_BYTES;
     ok = ok && make_map(&plan->map_a, g.A, eb, g.M, g.K, lda, slab_elems, p.block_k, mn_atom32);
+    if (x3) ok = ok && make_map(&plan->map_a_lo, g.A_lo, eb, g.M, g.K, lda, slab_elems, p.block_k, mn_atom32);
   } else {
     p.a_boxes = 1;
     p.a_box_bytes = BLOCK_M * SLAB_BYTES;
@@ -1216,6 +1277,7 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
     p.a_kstep = KSTEP_BYTES;
     p.a_layout = 2;
     ok = ok && make_map(&plan->map_a, g.A, eb, g.K, g.M, lda, p.block_k, BLOCK_M, false);
+    if (x3) ok = ok && make_map(&plan->map_a_lo, g.A_lo, eb, g.K, g.M, lda, p.block_k, BLOCK_M, false);
   }
   if (b_mn) {
     p.b_boxes = cta_bn / slab_elems;
@@ -1226,6 +1288,7 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
     p.b_layout = mn_layout;
     p.b_kstep = (KSTEP_BYTES / eb) * SLAB_BYTES;
     ok = ok && make_map(&plan->map_b, g.B, eb, g.N, g.K, ldb, slab_elems, p.block_k, mn_atom32);
+    if (x3) ok = ok && make_map(&plan->map_b_lo, g.B_lo, eb, g.N, g.K, ldb, slab_elems, p.block_k, mn_atom32);
   } else {
     p.b_boxes = 1;
     p.b_box_bytes = p.b_stage_bytes;
@@ -1234,11 +1297,17 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
     p.b_kstep = KSTEP_BYTES;
     p.b_layout = 2;
     ok = ok && make_map(&plan->map_b, g.B, eb, g.K, g.N, ldb, p.block_k, cta_bn, false);
+    if (x3) ok = ok && make_map(&plan->map_b_lo, g.B_lo, eb, g.K, g.N, ldb, p.block_k, cta_bn, false);
   }
   if (!ok) {
     delete plan;
     return fail("cuTensorMapEncodeTiled failed");
   }
+  if (!x3) {  // the kernel takes all six maps: unused ones are copies of valid ones
+    plan->map_a_lo = plan->map_a;
+    plan->map_b_lo = plan->map_b;
+  }
+  p.x3 = x3 ? 1 : 0;
   // Epilogue chunk buffers (32 rows x 128 bytes per buffer) behind the stages: one buffer per
   // epilogue warp in the 256-row mode (eight warps; three 64 KB stages fill the rest), two otherwise.
   memset(&plan->map_c, 0, sizeof plan->map_c);
@@ -1255,11 +1324,22 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
                       g.C, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                       CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         p.tma_store = 0;  // e.g. a row pitch beyond the tensor map's limits: direct stores serve it
+      plan->map_c_lo = plan->map_c;
+      if (p.tma_store && g.C_lo &&
+          enc(&plan->map_c_lo, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, g.C_lo, dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        p.tma_store = 0;
     }
+  }
+  p.c_lo = (g.C_lo && p.tma_store) ? 1 : 0;
+  if (g.C_lo && !p.c_lo) {
+    delete plan;
+    return fail("the result twin needs the TMA-store epilogue");
   }
   p.epi_bufs = (p.sub_m == 2 && !p.pair) ? 1 : 2;
   const size_t epi_bytes = p.tma_store ? (size_t)(p.pair ? 4 : 4 * p.sub_m) * p.epi_bufs * 4096 : 0;
-  const size_t stage = p.a_stage_bytes + p.b_stage_bytes;
+  const size_t stage = (size_t)(p.a_stage_bytes + p.b_stage_bytes) * (x3 ? 2 : 1);
   const size_t budget = 227 * 1024 - 1024 /* alignment slack */ - 512 /* static: barriers */;
   int stages = (int)((budget - epi_bytes) / stage);
   if (stages > MAX_STAGES) stages = MAX_STAGES;
@@ -1304,25 +1384,27 @@ bool gemm_tc_plan_set_mask(TcPlan* plan, uint32_t* mask_out, const uint32_t* mas
 }
 
 cudaError_t gemm_tc_launch(const TcPlan* plan, cudaStream_t stream, unsigned int* status) {
+  // the kernels' shared-memory limit is raised once per device; host threads that drive
+  // different GPUs may come here at the same time
+  static std::mutex attr_mutex;
   static unsigned long long attr_set = 0;  // one bit per device ordinal
   int dev = 0;
   cudaGetDevice(&dev);
-  if (!(attr_set >> (dev & 63) & 1ull)) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(gemm_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
-    if (e != cudaSuccess) return e;
-    attr_set |= 1ull << (dev & 63);
+  {
+    std::lock_guard<std::mutex> attr_lock(attr_mutex);
+    if (!(attr_set >> (dev & 63) & 1ull)) {
+      cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(gemm_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+      if (e != cudaSuccess) return e;
+      attr_set |= 1ull << (dev & 63);
+    }
   }
   TcParams p = plan->p;
   p.status = status;
   if (p.pair) {
-    static unsigned long long pair_attr_set = 0;
-    if (!(pair_attr_set >> (dev & 63) & 1ull)) {
-      cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
-      if (e != cudaSuccess) return e;
-      pair_attr_set |= 1ull << (dev & 63);
-    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(plan->grid);
     cfg.blockDim = dim3(NUM_THREADS);
@@ -1338,9 +1420,11 @@ cudaError_t gemm_tc_launch(const TcPlan* plan, cudaStream_t stream, unsigned int
     return cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel, plan->map_a, plan->map_b, plan->map_c, p);
   }
   if (p.sub_m == 2)
-    gemm_tc_kernel<2><<<plan->grid, NUM_THREADS_SUB2, plan->smem, stream>>>(plan->map_a, plan->map_b, plan->map_c, p);
+    gemm_tc_kernel<2><<<plan->grid, NUM_THREADS_SUB2, plan->smem, stream>>>(
+        plan->map_a, plan->map_b, plan->map_c, plan->map_a_lo, plan->map_b_lo, plan->map_c_lo, p);
   else
-    gemm_tc_kernel<1><<<plan->grid, NUM_THREADS, plan->smem, stream>>>(plan->map_a, plan->map_b, plan->map_c, p);
+    gemm_tc_kernel<1><<<plan->grid, NUM_THREADS, plan->smem, stream>>>(
+        plan->map_a, plan->map_b, plan->map_c, plan->map_a_lo, plan->map_b_lo, plan->map_c_lo, p);
   return cudaGetLastError();
 }
 

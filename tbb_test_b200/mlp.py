@@ -264,6 +264,13 @@ class MLP:
     def reset_timing(self):
         self._ck(self.lib.b2_reset_timing(self._h))
 
+    def site_report(self):
+        """(GEMM sites on the tensor-core kernel, sites on the CUDA-core kernel, reason of the first refusal)."""
+        a, b = C.c_int(), C.c_int()
+        buf = C.create_string_buffer(256)
+        self._ck(self.lib.b2_site_report(self._h, C.byref(a), C.byref(b), buf, 256))
+        return a.value, b.value, buf.value.decode()
+
     def launch_counts(self):
         a, b = C.c_longlong(), C.c_longlong()
         self._ck(self.lib.b2_launch_counts(self._h, C.byref(a), C.byref(b)))

@@ -43,7 +43,7 @@ FLOOR_FACTOR = 8.0
 
 def _prec(name):
     from tbb_test_b200 import _capi as K
-    return {"fp32": K.PREC_FP32, "tf32": K.PREC_TF32, "bf16": K.PREC_BF16}[name]
+    return {"fp32": K.PREC_FP32, "fp32tc": K.PREC_FP32_TC, "tf32": K.PREC_TF32, "bf16": K.PREC_BF16}[name]
 
 
 def _report(tag, out, floor=None):
@@ -58,7 +58,7 @@ SHAPES = {
 
 
 @pytest.mark.parametrize("cfg", sorted(SHAPES))
-@pytest.mark.parametrize("prec,tol", [("bf16", 5e-5), ("tf32", 2e-3), ("fp32", 2e-5)])
+@pytest.mark.parametrize("prec,tol", [("bf16", 5e-5), ("tf32", 2e-3), ("fp32", 2e-5), ("fp32tc", 2e-5)])
 def test_literal_shape_gemms(native, oracle, cfg, prec, tol):
     """Forward (ReLU epilogue), weight-gradient and input-gradient (mask epilogue) GEMM of one
     layer at the configuration's literal shape, on the oracle's operands."""
@@ -91,12 +91,15 @@ def test_literal_shape_gemms(native, oracle, cfg, prec, tol):
             assert rel_fro(dg, ref) <= tol
         total, tc = dev.launch_counts()
         assert (tc >= 3) == (prec != "fp32")
+        if prec == "fp32tc":  # same tolerance class as the CUDA-core fp32 kernel, per row as well
+            row = np.linalg.norm(wg - oracle.sgemm(True, False, dz, a), axis=1)
+            assert row.max() <= 1e-4 * np.linalg.norm(wg, axis=1).max()
     finally:
         oracle.use_builtin_gemm()
         dev.close()
 
 
-@pytest.mark.parametrize("prec", ["fp32", "bf16"])
+@pytest.mark.parametrize("prec", ["fp32", "fp32tc", "bf16"])
 def test_configuration_1_ten_iterations_from_shared_state(native, oracle, prec):
     """The 10 iterations of configuration 1, each started from the oracle's weights."""
     from tbb_test_b200 import _capi as K
@@ -107,7 +110,7 @@ def test_configuration_1_ten_iterations_from_shared_state(native, oracle, prec):
     # this configuration's own distance between two summation orders, measured once (step 1)
     _, _, floor = run_step_pair(oracle, nf, batch, _prec(prec), K.MODE_BASELINE, 1, 0.01, rounding=rounding,
                                 wdist=("uniform", 1.0 / 32), openblas=True, taps="weights", floor_ksplit=4)
-    tol = FP32_STEP if prec == "fp32" else SAME_ROUNDING_STEP
+    tol = FP32_STEP if prec in ("fp32", "fp32tc") else SAME_ROUNDING_STEP
     oracle.use_openblas()
     try:
         dev = MLP(nf, batch, precision=_prec(prec), lr=0.01)
@@ -141,7 +144,7 @@ def test_configuration_1_ten_iterations_from_shared_state(native, oracle, prec):
         oracle.use_builtin_gemm()
 
 
-@pytest.mark.parametrize("prec", ["fp32", "tf32", "bf16"])
+@pytest.mark.parametrize("prec", ["fp32", "fp32tc", "tf32", "bf16"])
 def test_configuration_1_ten_steps_free_running(native, oracle, prec):
     """10 steps without re-synchronisation: the loss agrees; the state is compared with loose
     bounds because differences between any two implementations feed themselves here."""
@@ -150,17 +153,18 @@ def test_configuration_1_ten_steps_free_running(native, oracle, prec):
                                      wdist=("uniform", 1.0 / 32), openblas=True)
     _report(f"c1 {prec} free running vs fp32 oracle", out)
     loss_d, loss_o = out["loss"][0][0], out["loss"][1][0]
-    assert abs(loss_d - loss_o) <= (1e-5 if prec == "fp32" else 1e-3) * abs(loss_o)
+    assert abs(loss_d - loss_o) <= (1e-5 if prec in ("fp32", "fp32tc") else 1e-3) * abs(loss_o)
     check_errors(out, dict(state=2e-2, total=2e-1, grad=3e-1))
     if prec != "fp32":
         assert tc >= 10 * 15, "the step did not run on the tensor-core kernels"
 
 
-def test_configuration_3_one_step_fp32(native, oracle):
+@pytest.mark.parametrize("prec", ["fp32", "fp32tc"])
+def test_configuration_3_one_step_fp32(native, oracle, prec):
     from tbb_test_b200 import _capi as K
-    out, _, floor = run_step_pair(oracle, [512] * 21, 2048, K.PREC_FP32, K.MODE_BASELINE, 1, 0.01,
+    out, _, floor = run_step_pair(oracle, [512] * 21, 2048, _prec(prec), K.MODE_BASELINE, 1, 0.01,
                                   wdist=("uniform", 512 ** -0.5), openblas=True, floor_ksplit=4)
-    _report("c3 fp32", out, floor)
+    _report(f"c3 {prec}", out, floor)
     check_errors(out, FP32_STEP, floor=floor, factor=FLOOR_FACTOR,
                  weights=problem_weights(oracle, [512] * 21, 2048, ("uniform", 512 ** -0.5)))
 

@@ -68,6 +68,27 @@ def test_bf16_tensor_core(dev, oracle, form, shape):
     assert rel_fro(c, ref) <= TOL["bf16_f32out"]
 
 
+@pytest.mark.parametrize("shape", SHAPES + [(4096, 1024, 136), (2048, 512, 512)], ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("form", list(FORMS))
+def test_fp32_class_tensor_core(dev, oracle, form, shape):
+    """B2_PREC_FP32_TC: three tf32 MMAs per k-step on operands split into high and low parts;
+    the fp32 bound of the CUDA-core kernel applies (and the plain tf32 kernel misses it by 30x)."""
+    from tbb_test_b200 import _capi as K
+    m, n, k = shape
+    ta, tb, a, b = operands(oracle, form, m, n, k, 23)
+    before = dev.launch_counts()[1]
+    c = dev.sgemm_host(K.PREC_FP32_TC, ta, tb, a, b)
+    assert dev.launch_counts()[1] == before + 1, "tensor-core kernel was not used"
+    oracle.use_openblas()
+    try:
+        ref = oracle.sgemm(ta, tb, a, b)
+    finally:
+        oracle.use_builtin_gemm()
+    assert rel_fro(c, ref) <= TOL["fp32"]
+    row_err = np.linalg.norm(c - ref, axis=1) / np.maximum(np.linalg.norm(ref, axis=1), 1e-30)
+    assert row_err.max() <= 1e-4
+
+
 # Shapes wide enough for the 256-row tile mode (two accumulators per CTA sharing each
 # B slab): an exact multiple of the tile grid, and a ragged one whose tile count leaves
 # a partial last wave that is handed out as 128-row halves.
@@ -98,14 +119,14 @@ def test_large_tile_mode(dev, oracle, form, shape, prec):
     assert row_err.max() <= (1e-4 if prec == "bf16" else 4e-3)
 
 
-@pytest.mark.parametrize("prec", ["fp32", "tf32", "bf16"])
+@pytest.mark.parametrize("prec", ["fp32", "fp32tc", "tf32", "bf16"])
 @pytest.mark.parametrize("shape", [(256, 512, 256), (104, 72, 136)], ids=lambda s: "x".join(map(str, s)))
 def test_relu_and_mask_epilogues(dev, oracle, prec, shape):
     from tbb_test_b200 import _capi as K
-    P = {"fp32": K.PREC_FP32, "tf32": K.PREC_TF32, "bf16": K.PREC_BF16}[prec]
+    P = {"fp32": K.PREC_FP32, "fp32tc": K.PREC_FP32_TC, "tf32": K.PREC_TF32, "bf16": K.PREC_BF16}[prec]
     m, n, k = shape
     rnd = oracle.round_bf16 if prec == "bf16" else (lambda x: x)
-    tol = {"fp32": TOL["fp32"], "tf32": TOL["tf32"], "bf16": TOL["bf16_bf16out"]}[prec]
+    tol = {"fp32": TOL["fp32"], "fp32tc": TOL["fp32"], "tf32": TOL["tf32"], "bf16": TOL["bf16_bf16out"]}[prec]
     # forward with fused ReLU
     ta, tb, a, b = operands(oracle, "fwd_NT", m, n, k, 41)
     c = dev.sgemm_host(P, ta, tb, a, b, epilogue=K.EPI_RELU)

@@ -33,6 +33,7 @@ from helpers import make_problem, rel_fro
 pytestmark = pytest.mark.gpu
 
 TOL = {"fp32": dict(state=2e-5, total=2e-5, grad=2e-5),
+       "fp32tc": dict(state=2e-5, total=2e-5, grad=2e-5),
        "tf32": dict(state=1e-2, total=5e-2, grad=1.5e-1),
        "bf16": dict(state=2e-2, total=1e-1, grad=2.5e-1)}
 SAME_ROUNDING_TOL = 2e-3
@@ -56,7 +57,7 @@ def check(out, tol, skip=()):
 
 def _prec(name):
     from tbb_test_b200 import _capi as K
-    return {"fp32": K.PREC_FP32, "tf32": K.PREC_TF32, "bf16": K.PREC_BF16}[name]
+    return {"fp32": K.PREC_FP32, "fp32tc": K.PREC_FP32_TC, "tf32": K.PREC_TF32, "bf16": K.PREC_BF16}[name]
 
 
 def run_pair(O, nf, batch, prec, mode, steps, lr, rounding=None, **kw):
@@ -92,7 +93,7 @@ def run_pair(O, nf, batch, prec, mode, steps, lr, rounding=None, **kw):
     return out, counts
 
 
-@pytest.mark.parametrize("prec", ["fp32", "tf32", "bf16"])
+@pytest.mark.parametrize("prec", ["fp32", "fp32tc", "tf32", "bf16"])
 def test_baseline_mode_10_steps(native, oracle, prec):
     """Config-1-shaped job scaled to 256 wide: ReLU MLP, +-1 targets, lr 0.01, 10 steps."""
     from tbb_test_b200 import _capi as K
@@ -122,24 +123,37 @@ def test_bf16_three_steps_against_rounding_oracle(native, oracle):
     check(out, dict(state=5e-3, total=3e-2, grad=1e-1))
 
 
-@pytest.mark.parametrize("prec", ["fp32", "tf32"])
+@pytest.mark.parametrize("prec", ["fp32", "fp32tc", "tf32"])
 def test_ref_mode_matches_reference_semantics(native, oracle, prec):
     """REF mode = the C++ reference as written: no ReLU, the forward output fed back
     as the gradient, tiny lr (mlp_omp.cc:565,609,655)."""
     from tbb_test_b200 import _capi as K
     nf = [128, 256, 128, 64]
     out, _ = run_pair(oracle, nf, 200, prec, K.MODE_REF, 4, 1e-6)
-    check(out, TOL["fp32"] if prec == "fp32" else dict(state=1e-2, total=1e-2, grad=1e-2))
+    check(out, TOL["fp32"] if prec in ("fp32", "fp32tc") else dict(state=1e-2, total=1e-2, grad=1e-2))
+
+
+def test_cuda_core_substitution_is_reported(native):
+    """A site the tensor-core kernel cannot address is served by the CUDA-core kernel - and says so."""
+    from tbb_test_b200 import _capi as K
+    from tbb_test_b200.mlp import MLP
+    m = MLP([128, 128, 1], 64, precision=K.PREC_BF16)
+    tc, cc, why = m.site_report()
+    assert tc > 0 and cc > 0 and "N < 16" in why
+    m.close()
+    m = MLP([128, 128, 128], 64, precision=K.PREC_BF16)
+    assert m.site_report()[1] == 0
+    m.close()
 
 
 def test_reference_topology_with_unit_tail(native, oracle):
     """The reference's own widths end in a 1-wide layer (mlp_bench_common.h:26)."""
     from tbb_test_b200 import _capi as K
     nf = [128, 128, 128, 1]
-    for prec in ("fp32", "bf16"):
+    for prec in ("fp32", "fp32tc", "bf16"):
         out, _ = run_pair(oracle, nf, 96, prec, K.MODE_REF, 2, 1e-8,
                           rounding=oracle.ROUND_BF16 if prec == "bf16" else None)
-        check(out, TOL["fp32"] if prec == "fp32" else SAME_ROUNDING_TOL)
+        check(out, TOL["fp32"] if prec != "bf16" else SAME_ROUNDING_TOL)
 
 
 @pytest.mark.parametrize("kw", [dict(overlap=False), dict(use_graph=True), dict(collect_timing=True),

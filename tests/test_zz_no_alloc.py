@@ -36,9 +36,12 @@ def test_noalloc_gemm_matches_allocating_entry_point_twice(native, oracle):
         tb_d = torch.from_numpy(b).cuda()
         tc_d = torch.full((m, n), float("nan"), device="cuda", dtype=torch.float32)
         torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()
         rc = lib.b2_gemm_bf16_noalloc(int(ta), int(tb), m, n, k, ta_d.data_ptr(), a.shape[1], tb_d.data_ptr(),
                                       b.shape[1], tc_d.data_ptr(), n, None)
         assert rc == K.OK, lib.b2_noalloc_last_error()
+        if seed != cases[0][2]:  # the first call on a device may load the kernels' module; later ones hold nothing new
+            assert torch.cuda.mem_get_info()[0] == free_before, "the call changed the device's free memory"
         got = tc_d.cpu().numpy()
         assert rel_fro(got, want) <= TOL
         ref = oracle.sgemm(ta, tb, oracle.round_bf16(a), oracle.round_bf16(b))
@@ -59,3 +62,7 @@ def test_noalloc_gemm_rejects_operands_beyond_the_fixed_scratch(native):
     assert rc == K.ERR_UNSUPPORTED
     assert b"at most" in lib.b2_noalloc_last_error()
     assert lib.b2_gemm_bf16_noalloc(0, 0, 0, n, k, a.data_ptr(), k, b.data_ptr(), n, c.data_ptr(), n, None) == K.ERR_INVALID
+    # a stored row length that is not a multiple of 8 elements cannot be repacked for TMA
+    assert lib.b2_gemm_bf16_noalloc(0, 0, 64, 64, 100, a.data_ptr(), 100, b.data_ptr(), 64, c.data_ptr(), 64,
+                                    None) == K.ERR_UNSUPPORTED
+    assert b"not served" in lib.b2_noalloc_last_error()
