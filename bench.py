@@ -349,7 +349,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS) + ["c2"],
                     help="c2 = the gradient-allreduce sweep alone (needs 2 or more GPUs)")
-    ap.add_argument("--precision", default="bf16", choices=["bf16", "tf32", "fp32"])
+    ap.add_argument("--precision", default="bf16", choices=["bf16", "tf32", "fp32", "fp32tc"],
+                    help="fp32tc = fp32-class results on the tensor cores (three tf32 MMAs on split operands)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--comm-sms", type=int, default=-1,
@@ -449,7 +450,7 @@ def main():
                               "error": what}))
         sys.exit(3)
 
-    prec = {"bf16": K.PREC_BF16, "tf32": K.PREC_TF32, "fp32": K.PREC_FP32}[args.precision]
+    prec = {"bf16": K.PREC_BF16, "tf32": K.PREC_TF32, "fp32": K.PREC_FP32, "fp32tc": K.PREC_FP32_TC}[args.precision]
 
     # ---- the reference's start-up self-check (mlp_omp.cc:325-373, 413-416) on every rank ---------
     # grad(s*R + i, j) = s + i + j, w = i*j, alpha = 1  ->  w = i*j - ((i + j)*N + N(N-1)/2), exact in fp32

@@ -46,7 +46,12 @@ struct GemmDesc {
   const void* A_lo;
   const void* B_lo;
   void* C_lo;
+  // Optional in-kernel timeline of the tensor-core kernel (null = off): CTA 0 stamps %globaltimer
+  // per tile into trace[tile * 4 + {0: first MMA issued, 1: accumulator complete (seen by the
+  // epilogue), 2: accumulator released, 3: last store of the tile issued}], up to TC_TRACE_TILES tiles.
+  unsigned long long* trace;
 };
+constexpr int TC_TRACE_TILES = 64;
 constexpr size_t TC_WS_SLOT_BYTES = 2 * 128 * 256 * sizeof(float);
 
 // CUDA-core GEMM for any shape, stride and alignment (fp32 accumulate).

@@ -515,6 +515,7 @@ bool bucket_sharded(const b2_handle* h, int low) {
 // shard_update only): each rank contributes the slices it owns.
 int gather_masters(b2_handle* h) {
   if (!h->masters_stale) return B2_OK;
+  if (!h->comm) return fail(h, B2_ERR_STATE, "the communicator of this job was aborted after an error");
   for (int l = h->L - 1; l >= 0; --l) {
     if (h->bucket_low[l] != l || !bucket_sharded(h, l)) continue;
     size_t begin, count;
@@ -549,6 +550,8 @@ int enqueue_step(b2_handle* h, bool timed, int slot = 0) {
   cudaStream_t su = overlap ? h->s_upd : h->s_main;
   const bool has_ar = h->cfg.world_size > 1 && h->cfg.allreduce;
   int rc;
+  if (has_ar && !h->comm)
+    return fail(h, B2_ERR_STATE, "the communicator of this job was aborted after an error; destroy the handles");
   int pending_ag = -1;  // bucket (its lowest layer) whose allgather is still to be issued
   CK(h, cudaMemsetAsync(loss_acc, 0, sizeof(double), sm));
   for (int l = 0; l < L; ++l) {
@@ -940,6 +943,31 @@ int b2_create(const b2_config* cfg, b2_handle** out) {
     h->bucket_high.assign(L, 0);
     plan_gradient_buckets(layer_bytes.data(), L, cfg->world_size, cfg->allreduce != 0, cfg->ar_bucket_mb, growth,
                           h->bucket_low.data(), h->bucket_high.data());
+    // B2_BUCKET_LAYERS=a,b,c,... (experiments): layers per bucket, from the last layer down; the
+    // counts must add up to the number of layers, else the variable is ignored
+    if (const char* e = getenv("B2_BUCKET_LAYERS")) {
+      std::vector<int> counts;
+      int sum = 0;
+      for (const char* q = e; *q;) {
+        int v = atoi(q);
+        if (v < 1) { sum = -1; break; }
+        counts.push_back(v);
+        sum += v;
+        while (*q && *q != ',') ++q;
+        if (*q == ',') ++q;
+      }
+      if (sum == L && cfg->world_size > 1 && cfg->allreduce) {
+        int high = L - 1;
+        for (int c : counts) {
+          const int low = high - c + 1;
+          for (int k = low; k <= high; ++k) {
+            h->bucket_low[k] = low;
+            h->bucket_high[k] = high;
+          }
+          high = low - 1;
+        }
+      }
+    }
   }
   TRY(dev_alloc(h, &h->y, bl * h->nf[L] * 4));
   TRY(dev_alloc(h, &h->target, bl * h->nf[L] * 4));
@@ -1384,6 +1412,8 @@ int b2_allreduce_sgd(b2_handle* h, int l) {
   LAYER_OK(h, l, h->L - 1);
   int rc;
   const bool has_ar = h->cfg.world_size > 1 && h->cfg.allreduce;
+  if (has_ar && !h->comm)
+    return fail(h, B2_ERR_STATE, "the communicator of this job was aborted after an error; destroy the handles");
   if (has_ar && h->bucket_low[l] == l && h->bucket_high[l] == l && bucket_sharded(h, l)) {
     // the layer is a bucket of its own: the reference's route (mlp_omp.cc:297-323)
     if ((rc = bucket_reduce_scatter(h, l, l, h->s_main, false))) return rc;
@@ -1753,6 +1783,12 @@ int b2_gemm_bench(b2_handle* h, int form, int m, int n, int k, int precision, in
   const bool x3 = precision == B2_PREC_FP32_TC && !h->cfg.force_simt;
   int rc = B2_OK;
   const bool tc = precision != B2_PREC_FP32 && !h->cfg.force_simt;
+  // B2_TC_TRACE=1: per-tile timeline of CTA 0 of the last timed launch, printed to stderr
+  unsigned long long* trace_dev = nullptr;
+  if (tc && getenv("B2_TC_TRACE")) {
+    cudaMalloc((void**)&trace_dev, TC_TRACE_TILES * 4 * sizeof(unsigned long long));
+    cudaMemset(trace_dev, 0, TC_TRACE_TILES * 4 * sizeof(unsigned long long));
+  }
   do {
     for (int i = 0; i < sets && rc == B2_OK; ++i) {
       Set& s = S[i];
@@ -1791,6 +1827,7 @@ int b2_gemm_bench(b2_handle* h, int form, int m, int n, int k, int precision, in
       d.ws = nullptr; d.ws_flags = nullptr;
       d.A_lo = s.a_lo; d.B_lo = s.b_lo;
       d.C_lo = (x3 && form != 1) ? s.c_lo : nullptr;  // like the step: activations and gradients get a twin
+      d.trace = trace_dev;
       if (tc) {
         char why[128] = "";
         s.plan = gemm_tc_plan_create(d, sms > 0 && sms <= h->sms ? sms : h->sms, why, sizeof why);
@@ -1826,8 +1863,19 @@ int b2_gemm_bench(b2_handle* h, int form, int m, int n, int k, int precision, in
     float ms = 0.f;
     cudaEventElapsedTime(&ms, h->ev_t0, h->ev_t1);
     if (ms_per_iter) *ms_per_iter = (double)ms / iters;
+    if (trace_dev) {
+      std::vector<unsigned long long> t(TC_TRACE_TILES * 4);
+      cudaMemcpy(t.data(), trace_dev, t.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
+      fprintf(stderr, "tile: first MMA -> accumulator complete | complete -> released | released -> last store issued | "
+                      "accumulator complete -> next tile's first MMA   (ns, CTA 0)\n");
+      for (int i = 0; i < TC_TRACE_TILES && t[i * 4 + 1]; ++i)
+        fprintf(stderr, "%3d: %8lld | %8lld | %8lld | %8lld\n", i, (long long)(t[i * 4 + 1] - t[i * 4]),
+                (long long)(t[i * 4 + 2] - t[i * 4 + 1]), (long long)(t[i * 4 + 3] - t[i * 4 + 2]),
+                (i + 1 < TC_TRACE_TILES && t[(i + 1) * 4]) ? (long long)(t[(i + 1) * 4] - t[i * 4 + 1]) : -1LL);
+    }
     rc = check_status(h);
   } while (0);
+  cudaFree(trace_dev);
   for (auto& s : S) {
     gemm_tc_plan_destroy(s.plan);
     cudaFree(s.a); cudaFree(s.b); cudaFree(s.c); cudaFree(s.x);

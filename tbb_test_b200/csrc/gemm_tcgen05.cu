@@ -51,6 +51,7 @@ constexpr int MAX_STAGES = 8;
 constexpr int NUM_THREADS = 192;       // producer warp + MMA warp + 4 epilogue warps
 constexpr int NUM_THREADS_SUB2 = 320;  // 256-row tiles: one group of 4 epilogue warps per 128-row accumulator
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+constexpr uint32_t X3_CORR_COLS = 256;  // fp32-class mode: TMEM column offset of the correction accumulators
 
 struct TcParams {
   int M, N, K;
@@ -92,7 +93,8 @@ struct TcParams {
   unsigned int* status;
   // Epilogue through shared memory + TMA stores (tensor map of C as third kernel argument):
   // every epilogue warp owns epi_bufs chunk buffers of 32 rows x 128 bytes behind the stages.
-  int tma_store, epi_bufs;
+  int tma_store, epi_bufs;  // tma_store: staged epilogue on (1) / direct per-lane stores (0)
+  int store_by_tma;         // staged epilogue: 1 = TMA stores, 0 = coalesced st.global read back from the buffer
   uint32_t epi_off;  // byte offset of the chunk buffers from the (aligned) start of shared memory
   // ReLU bit planes: one bit per element, row-major words of 32 columns. A forward epilogue
   // writes the plane of the activation it produces, the input-gradient epilogue of the layer
@@ -104,6 +106,8 @@ struct TcParams {
   // x3 = the stage holds A, A_lo, B, B_lo; c_lo = the epilogue also writes the low-order twin
   // of C (v - tf32(v)) for the GEMM that will read C as an operand
   int x3, c_lo;
+  void* C_lo;
+  unsigned long long* trace;  // see GemmDesc::trace
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -264,6 +268,10 @@ __device__ __forceinline__ void mma_issue(uint32_t d, uint64_t adesc, uint64_t b
 // twins of both slabs, alo16 / blo16 sixteen-byte units behind the slabs themselves, and every
 // k-step issues three MMAs: A*B, A*B_lo and A_lo*B (the tensor core truncates fp32 operands
 // to tf32, so A and B stand for their own high parts; A_lo*B_lo, 2^-22 of the product, is dropped).
+// The two correction products go to an accumulator of their own, X3_CORR_COLS TMEM columns
+// behind the main one, and the epilogue adds the two: the tensor core truncates when it adds
+// into an accumulator, a bias that grows with the number of additions, so the main sum should
+// see K/8 of them, not 3K/8 (measured at K = 4096: 3.0e-5 relative with one accumulator).
 template <int SUB_M, bool TF32, bool PAIR>
 __device__ __forceinline__ void issue_kblock(uint32_t tmem_d, uint64_t a_tmpl, uint64_t b_tmpl, uint32_t sa16,
                                              uint32_t sb16, uint32_t a_step16, uint32_t b_step16, uint32_t idesc,
@@ -280,8 +288,8 @@ __device__ __forceinline__ void issue_kblock(uint32_t tmem_d, uint64_t a_tmpl, u
         const uint32_t d = tmem_d + (uint32_t)i * block_n;
         mma_issue<TF32, PAIR>(d, adesc, bdesc, idesc, accumulate);
         if (TF32 && !PAIR && SUB_M == 1 && alo16 != 0) {
-          mma_issue<TF32, PAIR>(d, adesc, bdesc + (uint64_t)blo16, idesc, 1u);
-          mma_issue<TF32, PAIR>(d, adesc + (uint64_t)alo16, bdesc, idesc, 1u);
+          mma_issue<TF32, PAIR>(d + X3_CORR_COLS, adesc, bdesc + (uint64_t)blo16, idesc, accumulate);
+          mma_issue<TF32, PAIR>(d + X3_CORR_COLS, adesc + (uint64_t)alo16, bdesc, idesc, 1u);
         }
       }
     }
@@ -479,6 +487,44 @@ __device__ __forceinline__ uint32_t mask_from_values(const TcParams& p, int row,
   return m;
 }
 
+// A staged chunk (32 rows x 128 bytes, swizzled) to global memory with coalesced stores: the
+// warp reads the buffer back so that one instruction covers four whole 128-byte rows (lanes
+// 8i..8i+7 take the eight 16-byte pieces of one row) and writes them with st.global - four full
+// lines per instruction instead of 32 lines touched by 16 bytes each when every lane stores its
+// own row. These stores go through the load/store unit, not through the TMA queue, where a
+// store would wait behind the producer's loads of the next tile.
+__device__ __forceinline__ void store_chunk_rows(const TcParams& p, void* cbase, const uint8_t* cbuf, int row0,
+                                                 int col0, int lane) {
+  const int es = p.out_bf16 ? 2 : 4;
+  const int per_piece = 16 / es;  // elements per 16-byte piece
+  const int piece = lane & 7;
+  const int gcol = col0 + piece * per_piece;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int rr = 4 * i + (lane >> 3);
+    const uint4 v = *reinterpret_cast<const uint4*>(cbuf + rr * 128 + ((piece ^ (rr & 7)) << 4));
+    const int grow = row0 + rr;
+    if (grow < p.M && gcol < p.N) {
+      uint8_t* g = static_cast<uint8_t*>(cbase) + ((long long)grow * p.ldc + gcol) * es;
+      if (gcol + per_piece <= p.N) {
+        *reinterpret_cast<uint4*>(g) = v;
+      } else {  // ragged right edge: element by element
+        const int left = p.N - gcol;
+#pragma unroll
+        for (int wi = 0; wi < 4; ++wi) {
+          const uint32_t word = wi == 0 ? v.x : wi == 1 ? v.y : wi == 2 ? v.z : v.w;
+          if (es == 4) {
+            if (wi < left) reinterpret_cast<uint32_t*>(g)[wi] = word;
+          } else {
+            if (2 * wi < left) reinterpret_cast<uint16_t*>(g)[2 * wi] = (uint16_t)(word & 0xFFFFu);
+            if (2 * wi + 1 < left) reinterpret_cast<uint16_t*>(g)[2 * wi + 1] = (uint16_t)(word >> 16);
+          }
+        }
+      }
+    }
+  }
+}
+
 // One epilogue warp's 32 rows of one accumulator: rows row0 .. row0+31 (this lane: row0 + lane),
 // columns n0 .. n0 + block_n of C, accumulator at TMEM address `taddr` (lane quarter and first
 // column already applied). `release()` hands the accumulator back to the MMA warp; it is called
@@ -503,6 +549,12 @@ __device__ __forceinline__ void epilogue_rows_tma(const TcParams& p, const CUten
       const int c0 = col0 + half * 32;
       uint32_t r[32];
       tmem_ld32(taddr + (uint32_t)(ch * chunk_cols + half * 32), r);
+      if (p.x3) {  // main sum + sum of the two correction products (an fp32 add with rounding)
+        uint32_t r2[32];
+        tmem_ld32(taddr + X3_CORR_COLS + (uint32_t)(ch * chunk_cols + half * 32), r2);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
+      }
       if (last && (half == 1 || !p.out_bf16)) {
         tc_fence_before();
         __syncwarp();
@@ -533,26 +585,40 @@ __device__ __forceinline__ void epilogue_rows_tma(const TcParams& p, const CUten
       }
       if (p.mask_out && row < p.M && c0 < p.N) p.mask_out[(long long)row * p.ld_mask + (c0 >> 5)] = bits;
     }
-    // the chunk buffer is free once the store issued EPI_BUFS chunks ago has read it
-    if (lane == 0) bulk_wait_read<EPI_BUFS - 1>();
-    __syncwarp();
-    uint8_t* dst = buf + (size_t)buf_i * 4096 + (size_t)lane * 128;
-#pragma unroll
-    for (int j = 0; j < 8; ++j)  // 16-byte piece j of row `lane` sits at slot j ^ (lane & 7): 128-byte swizzle
-      *reinterpret_cast<uint4*>(dst + ((j ^ swz) << 4)) =
-          make_uint4(words[4 * j], words[4 * j + 1], words[4 * j + 2], words[4 * j + 3]);
-    fence_proxy_async_smem();
-    __syncwarp();
-    if (lane == 0 && row0 < p.M) {
-      tma_store_2d(tma_c, buf + (size_t)buf_i * 4096, col0, row0);
-      bulk_commit();
-    }
-    buf_i = (buf_i + 1 == EPI_BUFS) ? 0 : buf_i + 1;
-    if (p.c_lo) {
-      // fp32-class mode: the low-order twin of the chunk, v - tf32(v) (exact), through the next buffer
+    if (p.store_by_tma) {
+      // the chunk buffer is free once the store issued EPI_BUFS chunks ago has read it
       if (lane == 0) bulk_wait_read<EPI_BUFS - 1>();
       __syncwarp();
-      uint8_t* dst2 = buf + (size_t)buf_i * 4096 + (size_t)lane * 128;
+    }
+    uint8_t* cbuf = buf + (size_t)buf_i * 4096;
+    {
+      uint8_t* dst = cbuf + (size_t)lane * 128;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)  // 16-byte piece j of row `lane` sits at slot j ^ (lane & 7): 128-byte swizzle
+        *reinterpret_cast<uint4*>(dst + ((j ^ swz) << 4)) =
+            make_uint4(words[4 * j], words[4 * j + 1], words[4 * j + 2], words[4 * j + 3]);
+    }
+    if (p.store_by_tma) {
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0 && row0 < p.M) {
+        tma_store_2d(tma_c, cbuf, col0, row0);
+        bulk_commit();
+      }
+      buf_i = (buf_i + 1 == EPI_BUFS) ? 0 : buf_i + 1;
+    } else {
+      __syncwarp();
+      store_chunk_rows(p, p.C, cbuf, row0, col0, lane);
+      __syncwarp();  // every lane has read the buffer before it is written again
+    }
+    if (p.c_lo) {
+      // fp32-class mode: the low-order twin of the chunk, v - tf32(v) (exact), the same way
+      if (p.store_by_tma) {
+        if (lane == 0) bulk_wait_read<EPI_BUFS - 1>();
+        __syncwarp();
+      }
+      uint8_t* lbuf = buf + (size_t)buf_i * 4096;
+      uint8_t* dst2 = lbuf + (size_t)lane * 128;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         uint32_t lo[4];
@@ -563,13 +629,19 @@ __device__ __forceinline__ void epilogue_rows_tma(const TcParams& p, const CUten
         }
         *reinterpret_cast<uint4*>(dst2 + ((j ^ swz) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
       }
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0 && row0 < p.M) {
-        tma_store_2d(tma_c_lo, buf + (size_t)buf_i * 4096, col0, row0);
-        bulk_commit();
+      if (p.store_by_tma) {
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0 && row0 < p.M) {
+          tma_store_2d(tma_c_lo, lbuf, col0, row0);
+          bulk_commit();
+        }
+        buf_i = (buf_i + 1 == EPI_BUFS) ? 0 : buf_i + 1;
+      } else {
+        __syncwarp();
+        store_chunk_rows(p, p.C_lo, lbuf, row0, col0, lane);
+        __syncwarp();
       }
-      buf_i = (buf_i + 1 == EPI_BUFS) ? 0 : buf_i + 1;
     }
   }
 }
@@ -672,7 +744,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tma_a) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tma_b) : "memory");
-    if (p.tma_store) asm volatile("prefetch.tensormap [%0];" ::"l"(&tma_c) : "memory");
+    if (p.tma_store && p.store_by_tma) asm volatile("prefetch.tensormap [%0];" ::"l"(&tma_c) : "memory");
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)),
@@ -752,6 +824,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       const uint32_t block_n = (uint32_t)p.block_n;
       const bool tf32 = p.kind_tf32 != 0;
       const uint32_t alo16 = p.x3 ? a_stage16 : 0u, blo16 = p.x3 ? (p.b_stage_bytes >> 4) : 0u;
+      int trace_tile = 0;
       WorkIter wi;
       Work it;
       work_begin(p, wi);
@@ -762,6 +835,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         for (int kb = it.kb0; kb < it.kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 3u)) { ok = false; break; }
           tc_fence_after();
+          if (p.trace && blockIdx.x == 0 && kb == it.kb0 && trace_tile < TC_TRACE_TILES)
+            p.trace[trace_tile * 4 + 0] = globaltimer();
           const uint32_t sa16 = smem16 + (uint32_t)stage * stage16;
           if (tf32)
             issue_kblock<SUB_M, true, false>(tmem_d, a_tmpl, b_tmpl, sa16, sa16 + a_stage16 * lo_mul, a_step16, b_step16,
@@ -774,6 +849,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         }
         if (!ok) break;
         tc_commit(&acc_full_bar[acc]);   // accumulator complete -> epilogue
+        ++trace_tile;
         if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
       }
     }
@@ -787,6 +863,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     const int sub = (warp - 2) >> 2;  // each group of four epilogue warps drains one 128-row accumulator
     uint8_t* ebuf = smem + p.epi_off + (size_t)(warp - 2) * (EPI_BUFS * 4096);
     int ebuf_i = 0;
+    int epi_tile = 0;
     WorkIter wi;
     Work it;
     work_begin(p, wi);
@@ -796,13 +873,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       if (p.tma_store) {  // whole tiles only (no stream-K pieces)
         if (!mbar_wait(&acc_full_bar[acc], acc_phase, abort_flag, p.status, 4u)) break;
         tc_fence_after();
+        const bool tracing = p.trace && blockIdx.x == 0 && warp == 2 && lane == 0 && epi_tile < TC_TRACE_TILES;
+        if (tracing) p.trace[epi_tile * 4 + 1] = globaltimer();
         uint64_t* release_bar = &acc_empty_bar[acc];
         if (sub < it.sub) {
           epilogue_rows_tma<EPI_BUFS>(
               p, &tma_c, &tma_c_lo,
               tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * acc_cols + (uint32_t)(sub * p.block_n),
               it.m0 + sub * BLOCK_M + q * 32, n_blk * p.block_n, ebuf, ebuf_i, lane,
-              [&]() { if (lane == 0) mbar_arrive(release_bar); });
+              [&]() {
+                if (lane == 0) mbar_arrive(release_bar);
+                if (tracing) p.trace[epi_tile * 4 + 2] = globaltimer();
+              });
+          if (tracing) p.trace[epi_tile * 4 + 3] = globaltimer();
+          ++epi_tile;
         } else {  // half tile: this group's accumulator was not used
           tc_fence_before();
           __syncwarp();
@@ -883,7 +967,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
       if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
     }
-    if (p.tma_store && lane == 0) bulk_wait_all();  // the chunk buffers must outlive the stores that read them
+    if (p.tma_store && p.store_by_tma && lane == 0) bulk_wait_all();  // the chunk buffers must outlive the stores that read them
   }
 
   __syncwarp();
@@ -943,7 +1027,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tma_a) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tma_b) : "memory");
-    if (p.tma_store) asm volatile("prefetch.tensormap [%0];" ::"l"(&tma_c) : "memory");
+    if (p.tma_store && p.store_by_tma) asm volatile("prefetch.tensormap [%0];" ::"l"(&tma_c) : "memory");
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)),
@@ -1008,6 +1092,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       const uint32_t smem16 = smem_u32(smem) >> 4, stage16 = stage_bytes >> 4, a_stage16 = p.a_stage_bytes >> 4;
       const uint32_t a_step16 = p.a_kstep >> 4, b_step16 = p.b_kstep >> 4, idesc = p.idesc;
       const bool tf32 = p.kind_tf32 != 0;
+      int trace_tile = 0;
       for (int t = pair; t < num_tiles && ok; t += num_pairs) {
         if (!mbar_wait(&acc_empty_bar[acc], acc_phase ^ 1, abort_flag, p.status, 2u)) { ok = false; break; }
         tc_fence_after();
@@ -1015,6 +1100,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         for (int kb = 0; kb < p.num_k_blocks; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 3u)) { ok = false; break; }
           tc_fence_after();
+          if (p.trace && blockIdx.x == 0 && kb == 0 && trace_tile < TC_TRACE_TILES)
+            p.trace[trace_tile * 4 + 0] = globaltimer();
           const uint32_t sa16 = smem16 + (uint32_t)stage * stage16;
           if (tf32)
             issue_kblock<1, true, true>(tmem_d, a_tmpl, b_tmpl, sa16, sa16 + a_stage16, a_step16, b_step16, idesc,
@@ -1027,6 +1114,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         }
         if (!ok) break;
         tc_commit_pair(&acc_full_bar[acc]);
+        ++trace_tile;
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1;
       }
@@ -1038,15 +1126,23 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     uint32_t acc_phase = 0;
     uint8_t* ebuf = smem + p.epi_off + (size_t)(warp - 2) * (2 * 4096);
     int ebuf_i = 0;
+    int epi_tile = 0;
     for (int t = pair; t < num_tiles; t += num_pairs) {
       const Item it = decode_item<2>(t, num_tiles, p.num_m_blocks, p.num_n_blocks, p.raster_m, 1 << 30);
       if (!mbar_wait(&acc_full_bar[acc], acc_phase, abort_flag, p.status, 4u)) break;
       tc_fence_after();
       if (p.tma_store) {
         const uint32_t release_addr = map_to_cta(smem_u32(&acc_empty_bar[acc]), 0);
+        const bool tracing = p.trace && blockIdx.x == 0 && warp == 2 && lane == 0 && epi_tile < TC_TRACE_TILES;
+        if (tracing) p.trace[epi_tile * 4 + 1] = globaltimer();
         epilogue_rows_tma<2>(p, &tma_c, &tma_c, tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * p.block_n),
                              it.m0 + (int)rank * BLOCK_M + q * 32, it.n_blk * p.block_n, ebuf, ebuf_i, lane,
-                             [&]() { if (lane == 0) mbar_arrive_cluster(release_addr); });
+                             [&]() {
+                               if (lane == 0) mbar_arrive_cluster(release_addr);
+                               if (tracing) p.trace[epi_tile * 4 + 2] = globaltimer();
+                             });
+        if (tracing) p.trace[epi_tile * 4 + 3] = globaltimer();
+        ++epi_tile;
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1;
         continue;
@@ -1066,7 +1162,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
-    if (p.tma_store && lane == 0) bulk_wait_all();
+    if (p.tma_store && p.store_by_tma && lane == 0) bulk_wait_all();
   }
 
   __syncwarp();
@@ -1201,8 +1297,9 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
   // CTA pairs: a 256 x 256 tile per pair of SMs once there is a tile for every pair
   {
     const char* pe = getenv("B2_TC_PAIR");
-    const bool want = pe ? (pe[0] == '1') : false;
-    p.pair = (want && !x3 && bn == 256 && tiles(2 * BLOCK_M, bn) >= sm_count / 2) ? 1 : 0;
+    const bool want = pe ? (pe[0] == '1' || pe[0] == '2') : false;
+    const bool any_count = pe && pe[0] == '2';  // experiments: also when there are fewer tiles than CTA pairs
+    p.pair = (want && !x3 && bn == 256 && (any_count || tiles(2 * BLOCK_M, bn) >= sm_count / 2)) ? 1 : 0;
     if (p.pair) p.sub_m = 2;  // tile rows for the work decomposition: 128 per CTA of the pair
   }
   p.acc_stages = (p.sub_m == 2 && !p.pair) ? 1 : 2;
@@ -1210,6 +1307,7 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
   p.num_n_blocks = (g.N + bn - 1) / bn;
   p.num_k_blocks = (g.K + p.block_k - 1) / p.block_k;
   p.tmem_cols = 2 * bn < 32 ? 32 : 2 * bn;  // 128, 256 or 512: powers of two
+  if (x3) p.tmem_cols = 512;                // two main accumulators (bn <= 128) and, 256 columns on, their correction twins
   {
     // band height that makes a wave of sm_count tiles about square in elements of C
     const double aspect = (double)bn / (p.sub_m * BLOCK_M);
@@ -1312,9 +1410,15 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
   // epilogue warp in the 256-row mode (eight warps; three 64 KB stages fill the rest), two otherwise.
   memset(&plan->map_c, 0, sizeof plan->map_c);
   {
+    // staged epilogue unless stream-K pieces are in play (B2_TC_EPILOGUE=direct: per-lane stores);
+    // the staged chunks leave by TMA stores, or with B2_TC_TMA_STORE=0 by coalesced st.global read
+    // back from the buffer (measured at 8192 x 4096 x 4096: 7.2 us against 8.2-10 us from the
+    // accumulator's completion to its release)
+    const char* ee = getenv("B2_TC_EPILOGUE");
     const char* e = getenv("B2_TC_TMA_STORE");
-    p.tma_store = (!p.streamk && !(e && e[0] == '0')) ? 1 : 0;
-    if (p.tma_store) {
+    p.tma_store = (!p.streamk && !(ee && ee[0] == 'd')) ? 1 : 0;
+    p.store_by_tma = (p.tma_store && !(e && e[0] == '0')) ? 1 : 0;
+    if (p.store_by_tma) {
       EncodeTiledFn enc = get_encode();
       cuuint64_t dims[2] = {(cuuint64_t)g.N, (cuuint64_t)g.M};
       cuuint64_t strides[1] = {(cuuint64_t)g.ldc * ob};
@@ -1323,19 +1427,20 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
       if (!enc || enc(&plan->map_c, ob == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
                       g.C, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                       CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        p.tma_store = 0;  // e.g. a row pitch beyond the tensor map's limits: direct stores serve it
+        p.store_by_tma = 0;  // e.g. a row pitch beyond the tensor map's limits
       plan->map_c_lo = plan->map_c;
-      if (p.tma_store && g.C_lo &&
+      if (p.store_by_tma && g.C_lo &&
           enc(&plan->map_c_lo, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, g.C_lo, dims, strides, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        p.tma_store = 0;
+        p.store_by_tma = 0;
     }
   }
   p.c_lo = (g.C_lo && p.tma_store) ? 1 : 0;
+  p.C_lo = g.C_lo;
   if (g.C_lo && !p.c_lo) {
     delete plan;
-    return fail("the result twin needs the TMA-store epilogue");
+    return fail("the result twin needs the staged epilogue");
   }
   p.epi_bufs = (p.sub_m == 2 && !p.pair) ? 1 : 2;
   const size_t epi_bytes = p.tma_store ? (size_t)(p.pair ? 4 : 4 * p.sub_m) * p.epi_bufs * 4096 : 0;
@@ -1361,6 +1466,7 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
   p.mask_out = nullptr;
   p.mask_in = nullptr;
   p.ld_mask = 0;
+  p.trace = g.trace;
   plan->grid = p.num_items < sm_count ? p.num_items : sm_count;
   if (p.streamk) plan->grid = sm_count;
   if (p.pair) {

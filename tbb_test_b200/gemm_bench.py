@@ -1,6 +1,6 @@
 """Times the GEMMs of one layer alone, per call form, at a given shape (one GPU).
 
-    python -m tbb_test_b200.gemm_bench --batch 8192 --width 4096 [--precision bf16|tf32]
+    python -m tbb_test_b200.gemm_bench --batch 8192 --width 4096 [--precision bf16|tf32|fp32tc|fp32]
                                        [--forms fwd,wgrad,dgrad] [--iters 20] [--sms 0]
                                        [--grad-bf16]
 
@@ -24,7 +24,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--batch", type=int, default=8192)
     ap.add_argument("--width", type=int, default=4096)
-    ap.add_argument("--precision", default="bf16", choices=["bf16", "tf32", "fp32"])
+    ap.add_argument("--precision", default="bf16", choices=["bf16", "tf32", "fp32", "fp32tc"])
     ap.add_argument("--forms", default="fwd,wgrad,dgrad")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
@@ -33,7 +33,7 @@ def main():
     args = ap.parse_args()
     from tbb_test_b200 import _capi as K
     from tbb_test_b200.mlp import MLP
-    prec = {"bf16": K.PREC_BF16, "tf32": K.PREC_TF32, "fp32": K.PREC_FP32}[args.precision]
+    prec = {"bf16": K.PREC_BF16, "tf32": K.PREC_TF32, "fp32": K.PREC_FP32, "fp32tc": K.PREC_FP32_TC}[args.precision]
     op = K.DTYPE_BF16 if args.precision == "bf16" else K.DTYPE_F32
     b, f = args.batch, args.width
     peak = None

@@ -264,8 +264,24 @@ int main(int argc, char** argv) {
   report_timing();
   printf("samples/s %g\n", (double)batch_size * NITER / wall_clock_time);
 
-  // final weights of replica 0 for the checksum (mlp_bench_common.cc:152-168)
-  for (int l = 0; l < nlayers; ++l) b2_download_weights(ws[0].h, l, weights[l]->rawData(), weights[l]->ld());
+  // final weights of replica 0 for the checksum (mlp_bench_common.cc:152-168). Every GPU takes
+  // part in the download: with the sharded update in BF16 precision it is a collective that first
+  // gathers the fp32 master weights from the ranks that own them; only replica 0's copy is kept.
+  ok = on_all_gpus(ws, [&](int g) -> int {
+    std::vector<float> scratch;
+    for (int l = 0; l < nlayers; ++l) {
+      int rc;
+      if (g == 0) {
+        rc = b2_download_weights(ws[g].h, l, weights[l]->rawData(), weights[l]->ld());
+      } else {
+        scratch.resize((size_t)nfeatures[l + 1] * nfeatures[l]);
+        rc = b2_download_weights(ws[g].h, l, scratch.data(), (size_t)nfeatures[l]);
+      }
+      if (rc) return rc;
+    }
+    return 0;
+  });
+  if (!ok) return 2;
   print_checksum();
   for (auto& w : ws) b2_destroy(w.h);
   return 0;

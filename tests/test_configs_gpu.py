@@ -37,6 +37,9 @@ pytestmark = pytest.mark.gpu
 # in either order, so of configuration 1's 4 M masked elements about 2 * 2e-6 * 0.7 * 4e6 = 10
 # have the other sign in the other order, each worth about 3e-4 of a weight gradient.
 FP32_STEP = dict(state=2e-5, total=1e-2, grad=1e-2)
+# fp32-class tensor-core mode: 2e-5 per GEMM; over the layers of a step the truncating accumulation of the
+# tensor core adds up as a bias (20 layers of configuration 3: 2.6e-5 on the output)
+FP32TC_STEP = dict(state=1e-4, total=1e-2, grad=1e-2)
 SAME_ROUNDING_STEP = dict(state=2e-3, total=2e-3, grad=2e-3)
 FLOOR_FACTOR = 8.0
 
@@ -110,7 +113,7 @@ def test_configuration_1_ten_iterations_from_shared_state(native, oracle, prec):
     # this configuration's own distance between two summation orders, measured once (step 1)
     _, _, floor = run_step_pair(oracle, nf, batch, _prec(prec), K.MODE_BASELINE, 1, 0.01, rounding=rounding,
                                 wdist=("uniform", 1.0 / 32), openblas=True, taps="weights", floor_ksplit=4)
-    tol = FP32_STEP if prec in ("fp32", "fp32tc") else SAME_ROUNDING_STEP
+    tol = {"fp32": FP32_STEP, "fp32tc": FP32TC_STEP}.get(prec, SAME_ROUNDING_STEP)
     oracle.use_openblas()
     try:
         dev = MLP(nf, batch, precision=_prec(prec), lr=0.01)
@@ -153,7 +156,7 @@ def test_configuration_1_ten_steps_free_running(native, oracle, prec):
                                      wdist=("uniform", 1.0 / 32), openblas=True)
     _report(f"c1 {prec} free running vs fp32 oracle", out)
     loss_d, loss_o = out["loss"][0][0], out["loss"][1][0]
-    assert abs(loss_d - loss_o) <= (1e-5 if prec in ("fp32", "fp32tc") else 1e-3) * abs(loss_o)
+    assert abs(loss_d - loss_o) <= {"fp32": 1e-5, "fp32tc": 1e-4}.get(prec, 1e-3) * abs(loss_o)
     check_errors(out, dict(state=2e-2, total=2e-1, grad=3e-1))
     if prec != "fp32":
         assert tc >= 10 * 15, "the step did not run on the tensor-core kernels"
@@ -165,7 +168,7 @@ def test_configuration_3_one_step_fp32(native, oracle, prec):
     out, _, floor = run_step_pair(oracle, [512] * 21, 2048, _prec(prec), K.MODE_BASELINE, 1, 0.01,
                                   wdist=("uniform", 512 ** -0.5), openblas=True, floor_ksplit=4)
     _report(f"c3 {prec}", out, floor)
-    check_errors(out, FP32_STEP, floor=floor, factor=FLOOR_FACTOR,
+    check_errors(out, FP32_STEP if prec == "fp32" else FP32TC_STEP, floor=floor, factor=FLOOR_FACTOR,
                  weights=problem_weights(oracle, [512] * 21, 2048, ("uniform", 512 ** -0.5)))
 
 
