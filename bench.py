@@ -52,7 +52,7 @@ WORKLOADS = {
 }
 
 
-def gradient_buckets(layer_bytes, world, bucket_mb):
+def gradient_buckets(layer_bytes, world, bucket_mb, sharded=False):
     """Bytes of each gradient collective of one step, in issue order, from the library's own
     rule (csrc/bucket_plan.h through the host library)."""
     import ctypes as C
@@ -61,7 +61,10 @@ def gradient_buckets(layer_bytes, world, bucket_mb):
     n = len(layer_bytes)
     low, high = (C.c_int * n)(), (C.c_int * n)()
     growth = float(os.environ.get("B2_BUCKET_GROWTH", 0.0))
-    H.b2h_plan_buckets((C.c_size_t * n)(*layer_bytes), n, world, 1, bucket_mb, C.c_double(growth), low, high)
+    if sharded:
+        H.b2h_plan_buckets_sharded((C.c_size_t * n)(*layer_bytes), n, world, bucket_mb, C.c_double(growth), low, high)
+    else:
+        H.b2h_plan_buckets((C.c_size_t * n)(*layer_bytes), n, world, 1, bucket_mb, C.c_double(growth), low, high)
     out, l = [], n - 1
     while l >= 0:
         out.append(sum(layer_bytes[low[l]:high[l] + 1]))
@@ -592,7 +595,7 @@ def main():
         es = 2 if args.grad_bf16 else 4
         ws = 2 if args.precision == "bf16" else 4  # bytes per weight the allgather carries
         shard = args.shard_update != 0
-        buckets = gradient_buckets([nf[l] * nf[l + 1] * es for l in range(L)], world, args.bucket_mb)
+        buckets = gradient_buckets([nf[l] * nf[l + 1] * es for l in range(L)], world, args.bucket_mb, sharded=shard)
         t_alone, wire = 0.0, 0.0
         for b in buckets:
             cnt = (b // es + 128 * world - 1) // (128 * world) * (128 * world)
@@ -653,9 +656,19 @@ def main():
         e2e_loss = pipelined(args.steps)
         torch.cuda.synchronize()
         dt = max_over_ranks(time.perf_counter() - t0)
+        # the host link alone: every rank copies its rows of the pinned input matrix, all ranks at once
+        barrier()
+        t1 = time.perf_counter()
+        for _ in range(5):
+            dev.upload_input(x_host)
+        h2d_s = max_over_ranks((time.perf_counter() - t1) / 5)
         e2e = {"value": batch * args.steps / dt, "unit": "samples/s",
                "h2d_bytes_per_step": batch * (nf[0] + nf[-1]) * 4, "d2h_bytes_per_step": 8 * world,
                "ms_per_step": dt / args.steps * 1e3, "loss_share_rank0": e2e_loss,
+               "h2d_alone_gbs_all_gpus": batch * nf[0] * 4 / h2d_s / 1e9,
+               "h2d_alone_note": "input rows only, pinned memory, every rank copying at the same time "
+                                 "(incl. the bf16 conversion kernel): the host link's share of a step is "
+                                 "h2d_bytes_per_step / this rate",
                "call": "b2_train_step_host_async + b2_wait_loss, fp32 host matrices in pinned memory"}
 
     cpu = None

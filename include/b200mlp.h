@@ -86,7 +86,7 @@ typedef struct {
   int comm_sms;             /* SMs the persistent GEMM kernels leave free for the collective's CTAs
                                while allreduce and GEMMs overlap (the counterpart of the threads the
                                reference takes away from the GEMMs, mlp_bench_common.h:40-48);
-                               -1 = default: 0 for one GPU, 20 otherwise */
+                               -1 = default: 20 on 4 or more GPUs, 0 otherwise */
   int ar_bucket_mb;         /* gradient allreduce granularity: 0 = one collective per layer, issued as
                                soon as that layer's weight gradient is done (what the reference does per
                                layer, mlp_omp.cc:692-705); N > 0 = consecutive layers are summed

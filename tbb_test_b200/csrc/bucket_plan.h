@@ -45,6 +45,17 @@ inline void plan_gradient_buckets(const size_t* layer_bytes, int nlayers, int wo
   }
 }
 
+// Sharded update (reduce-scatter, SGD on the owned slice, allgather): the step ends with the three
+// of them for the bucket that holds layer 0, which nothing can overlap - its gradient is the last
+// one produced and its weights are the first ones the next forward pass needs. Layer 0 therefore
+// gets a bucket of its own (the rest of its former bucket stays together).
+inline void plan_split_lowest_layer(int nlayers, int* bucket_low, int* bucket_high) {
+  if (nlayers < 2 || bucket_high[0] == 0) return;
+  const int high = bucket_high[0];
+  for (int k = 1; k <= high; ++k) bucket_low[k] = 1;
+  bucket_high[0] = 0;
+}
+
 // Layout of the gradient slab and of the weight slabs that mirror it: layers in the order
 // backward produces their gradients (L-1 first), each padded to a multiple of 128 * world_size
 // elements, so that every layer starts on a 256-byte boundary in a bf16 slab and every bucket

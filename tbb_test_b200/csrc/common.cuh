@@ -52,6 +52,7 @@ struct GemmDesc {
   unsigned long long* trace;
 };
 constexpr int TC_TRACE_TILES = 64;
+constexpr int TC_TRACE_WORDS = TC_TRACE_TILES * 4 + 64;  // + 8 chunks x 8 stamps of the first tile's epilogue
 constexpr size_t TC_WS_SLOT_BYTES = 2 * 128 * 256 * sizeof(float);
 
 // CUDA-core GEMM for any shape, stride and alignment (fp32 accumulate).

@@ -73,6 +73,11 @@ struct b2_handle {
   float* w_lo_slab = nullptr;
   std::vector<float*> w_lo, act_lo, dz_lo;
   float* act0_alt_lo = nullptr;
+  // B2_NCCL_UB=1 (2 or more GPUs): the gradient and weight slabs come from ncclMemAlloc and are
+  // registered with the communicator, so that its collectives run on them in place
+  bool nccl_ub = false;
+  void* ub_handle[3] = {nullptr, nullptr, nullptr};
+  bool ag_deferred = true;     // allgathers behind all reduce-scatters of a step, lowest bucket first
   bool shard = false;          // reduce-scatter + owned-slice SGD + allgather instead of allreduce + full SGD
   bool masters_stale = false;  // BF16 precision with shard: ranks hold current fp32 masters only for their slices
   std::vector<size_t> dw_pad;  // padded element count of layer l in the slabs (multiple of 128 * world)
@@ -553,6 +558,15 @@ int enqueue_step(b2_handle* h, bool timed, int slot = 0) {
   if (has_ar && !h->comm)
     return fail(h, B2_ERR_STATE, "the communicator of this job was aborted after an error; destroy the handles");
   int pending_ag = -1;  // bucket (its lowest layer) whose allgather is still to be issued
+  // Allgathers are issued behind ALL reduce-scatters of the step, lowest layers first: the next
+  // forward pass needs layer 0 first and the top layers last, while backward produced the
+  // gradients in the opposite order. So once the last gradient exists the collective stream
+  // only has to finish reduce-scatter + allgather of the LOWEST bucket before fwd(0) may start;
+  // the allgathers of the upper buckets run under the next forward pass. (B2_AG_ORDER=eager:
+  // each bucket's allgather right behind the next bucket's reduce-scatter, top bucket first.)
+  const bool ag_deferred = h->ag_deferred;
+  int deferred[64];
+  int ndeferred = 0;
   CK(h, cudaMemsetAsync(loss_acc, 0, sizeof(double), sm));
   for (int l = 0; l < L; ++l) {
     if (overlap && h->upd_pending[l]) {
@@ -594,6 +608,10 @@ int enqueue_step(b2_handle* h, bool timed, int slot = 0) {
       // before (its owned-slice SGD ran while this reduce-scatter was in flight)
       if ((rc = bucket_reduce_scatter(h, l, h->bucket_high[l], sc, timed))) return rc;
       if (overlap) CK(h, cudaEventRecord(h->ev_ar[l], sc));
+      if (pending_ag >= 0 && ag_deferred && ndeferred < 64) {
+        deferred[ndeferred++] = pending_ag;
+        pending_ag = -1;
+      }
       if (pending_ag >= 0) {
         if (overlap) CK(h, cudaStreamWaitEvent(sc, h->ev_shard[pending_ag], 0));
         if ((rc = bucket_allgather(h, pending_ag, h->bucket_high[pending_ag], sc, timed))) return rc;
@@ -641,10 +659,13 @@ int enqueue_step(b2_handle* h, bool timed, int slot = 0) {
       }
     }
   }
-  if (pending_ag >= 0) {  // the allgather of the last bucket
-    if (overlap) CK(h, cudaStreamWaitEvent(sc, h->ev_shard[pending_ag], 0));
-    if ((rc = bucket_allgather(h, pending_ag, h->bucket_high[pending_ag], sc, timed))) return rc;
-    for (int k = pending_ag; k <= h->bucket_high[pending_ag]; ++k) {
+  // the allgather of the last (lowest) bucket, then the deferred ones from the lowest layers up
+  for (int i = ndeferred; i >= 0; --i) {
+    const int b = (i == ndeferred) ? pending_ag : deferred[i];
+    if (b < 0) continue;
+    if (overlap) CK(h, cudaStreamWaitEvent(sc, h->ev_shard[b], 0));
+    if ((rc = bucket_allgather(h, b, h->bucket_high[b], sc, timed))) return rc;
+    for (int k = b; k <= h->bucket_high[b]; ++k) {
       if (overlap) {
         CK(h, cudaEventRecord(h->ev_upd[k], sc));
         h->upd_pending[k] = 1;
@@ -686,13 +707,24 @@ void free_all(b2_handle* h) {
     cudaStreamDestroy(h->s_wg);
   }
   if (h->ev_dz_last) cudaEventDestroy(h->ev_dz_last);
-  if (h->comm && nccl_api().ok) nccl_api().CommDestroy(h->comm);
+  if (h->comm && nccl_api().ok) {
+    for (void* rh : h->ub_handle)
+      if (rh && nccl_api().CommDeregister) nccl_api().CommDeregister(h->comm, rh);
+    nccl_api().CommDestroy(h->comm);
+  }
   if (h->graph_exec) cudaGraphExecDestroy(h->graph_exec);
   for (auto& s : h->fwd) gemm_tc_plan_destroy(s.plan);
   for (auto& s : h->wgrad) gemm_tc_plan_destroy(s.plan);
   for (auto& s : h->dgrad) gemm_tc_plan_destroy(s.plan);
-  cudaFree(h->w_slab);
-  cudaFree(h->w16_slab);
+  if (h->nccl_ub && nccl_api().MemFree) {
+    if (h->w_slab) nccl_api().MemFree(h->w_slab);
+    if (h->w16_slab) nccl_api().MemFree(h->w16_slab);
+    if (h->dw_slab) nccl_api().MemFree(h->dw_slab);
+    h->dw_slab = nullptr;
+  } else {
+    cudaFree(h->w_slab);
+    cudaFree(h->w16_slab);
+  }
   cudaFree(h->w_lo_slab);
   for (auto p : h->act_lo) cudaFree(p);
   for (auto p : h->dz_lo) cudaFree(p);
@@ -860,7 +892,9 @@ int b2_create(const b2_config* cfg, b2_handle** out) {
   h->sms = prop.multiProcessorCount;
   {
     const bool comm = cfg->world_size > 1 && cfg->allreduce && cfg->overlap;
-    int reserve = cfg->comm_sms < 0 ? (comm ? 20 : 0) : cfg->comm_sms;
+    // default: 20 on 4 or more GPUs, none on 2 (measured there: 3.28 ms per step of configuration 4
+    // with none against 3.36 ms with 20; on 8 GPUs 2.07 against 2.09)
+    int reserve = cfg->comm_sms < 0 ? (comm && cfg->world_size >= 4 ? 20 : 0) : cfg->comm_sms;
     if (reserve > h->sms / 2) reserve = h->sms / 2;
     h->gemm_sms = h->sms - reserve;
     h->cfg.comm_sms = reserve;
@@ -919,8 +953,20 @@ int b2_create(const b2_config* cfg, b2_handle** out) {
     std::vector<size_t> layer_elems(L);
     for (int l = 0; l < L; ++l) layer_elems[l] = (size_t)h->nf[l + 1] * h->nf[l];
     const size_t total = plan_slab_layout(layer_elems.data(), L, cfg->world_size, h->dw_off.data(), h->dw_pad.data());
-    TRY(dev_alloc(h, &h->w_slab, total * 4));
-    if (h->op_type == T_BF16) TRY(dev_alloc(h, &h->w16_slab, total * 2));
+    {
+      const char* ub = getenv("B2_NCCL_UB");
+      h->nccl_ub = ub && ub[0] == '1' && cfg->world_size > 1 && cfg->allreduce && nccl_api().ok &&
+                   nccl_api().MemAlloc && nccl_api().MemFree && nccl_api().CommRegister && nccl_api().CommDeregister;
+    }
+    auto slab_alloc = [&](void** ptr, size_t bytes) -> int {
+      if (!h->nccl_ub) return dev_alloc(h, reinterpret_cast<char**>(ptr), bytes);
+      if (nccl_api().MemAlloc(ptr, bytes) != ncclSuccess) return fail(h, B2_ERR_NCCL, "ncclMemAlloc of %zu bytes failed", bytes);
+      cudaError_t e_ = cudaMemset(*ptr, 0, bytes);
+      if (e_ != cudaSuccess) return fail(h, B2_ERR_CUDA, "cudaMemset: %s", cudaGetErrorString(e_));
+      return B2_OK;
+    };
+    TRY(slab_alloc(reinterpret_cast<void**>(&h->w_slab), total * 4));
+    if (h->op_type == T_BF16) TRY(slab_alloc(reinterpret_cast<void**>(&h->w16_slab), total * 2));
     if (h->x3) TRY(dev_alloc(h, &h->w_lo_slab, total * 4));
     for (int l = 0; l < L; ++l) {
       h->w[l] = h->w_slab + h->dw_off[l];
@@ -930,7 +976,7 @@ int b2_create(const b2_config* cfg, b2_handle** out) {
     h->shard = cfg->world_size > 1 && cfg->allreduce && cfg->shard_update != 0;
     h->p2p_flags_off = (total * es + 255) / 256 * 256;
     h->slab_bytes = h->p2p_flags_off + 256;  // zero-filled flag block (P2P_FLAG_BYTES) behind the gradients
-    TRY(dev_alloc(h, &h->dw_slab, h->slab_bytes));
+    TRY(slab_alloc(&h->dw_slab, h->slab_bytes));
     TRY(dev_alloc(h, &h->p2p_ctas_done, sizeof(unsigned int)));
     for (int l = 0; l < L; ++l) h->dw[l] = static_cast<char*>(h->dw_slab) + h->dw_off[l] * es;
     // buckets of consecutive layers (rule and rationale: bucket_plan.h); B2_BUCKET_GROWTH
@@ -943,6 +989,15 @@ int b2_create(const b2_config* cfg, b2_handle** out) {
     h->bucket_high.assign(L, 0);
     plan_gradient_buckets(layer_bytes.data(), L, cfg->world_size, cfg->allreduce != 0, cfg->ar_bucket_mb, growth,
                           h->bucket_low.data(), h->bucket_high.data());
+    {
+      const char* e = getenv("B2_AG_ORDER");
+      h->ag_deferred = !(e && e[0] == 'e');
+      // layer 0 in a bucket of its own (bucket_plan.h) unless the bucket size was given explicitly
+      // (ar_bucket_mb >= 0) or B2_SPLIT_LAST=0
+      const char* sl = getenv("B2_SPLIT_LAST");
+      if (h->shard && cfg->ar_bucket_mb < 0 && !(sl && sl[0] == '0'))
+        plan_split_lowest_layer(L, h->bucket_low.data(), h->bucket_high.data());
+    }
     // B2_BUCKET_LAYERS=a,b,c,... (experiments): layers per bucket, from the last layer down; the
     // counts must add up to the number of layers, else the variable is ignored
     if (const char* e = getenv("B2_BUCKET_LAYERS")) {
@@ -1040,6 +1095,16 @@ int b2_create(const b2_config* cfg, b2_handle** out) {
       r = n.CommInitRank(&h->comm, cfg->world_size, id, cfg->rank);
     }
     if (r != ncclSuccess) TRY(fail(h, B2_ERR_NCCL, "ncclCommInitRank failed: %s", n.GetErrorString(r)));
+    if (h->nccl_ub) {
+      const size_t es_ = esize(h->grad_type);
+      size_t welems = 0;
+      for (int l = 0; l < L; ++l) welems += h->dw_pad[l];
+      (void)es_;
+      if (n.CommRegister(h->comm, h->dw_slab, h->slab_bytes, &h->ub_handle[0]) != ncclSuccess ||
+          n.CommRegister(h->comm, h->w_slab, welems * 4, &h->ub_handle[1]) != ncclSuccess ||
+          (h->w16_slab && n.CommRegister(h->comm, h->w16_slab, welems * 2, &h->ub_handle[2]) != ncclSuccess))
+        TRY(fail(h, B2_ERR_NCCL, "ncclCommRegister failed"));
+    }
   }
   TRY(build_sites(h));
   TRYCK(cudaDeviceSynchronize());
@@ -1468,6 +1533,7 @@ int b2_p2p_describe(b2_handle* h, void* desc) {
   if (h->cfg.world_size < 2 || h->cfg.world_size > P2P_MAX_RANKS)
     return fail(h, B2_ERR_UNSUPPORTED, "the peer-memory path serves 2 to %d ranks", P2P_MAX_RANKS);
   if (h->grad_type != T_F32) return fail(h, B2_ERR_UNSUPPORTED, "the peer-memory path sums fp32 gradients only");
+  if (h->nccl_ub) return fail(h, B2_ERR_UNSUPPORTED, "the peer-memory path cannot share slabs allocated by NCCL (B2_NCCL_UB)");
   P2pDesc d;
   memset(&d, 0, sizeof d);
   d.magic = P2P_MAGIC;
@@ -1786,8 +1852,8 @@ int b2_gemm_bench(b2_handle* h, int form, int m, int n, int k, int precision, in
   // B2_TC_TRACE=1: per-tile timeline of CTA 0 of the last timed launch, printed to stderr
   unsigned long long* trace_dev = nullptr;
   if (tc && getenv("B2_TC_TRACE")) {
-    cudaMalloc((void**)&trace_dev, TC_TRACE_TILES * 4 * sizeof(unsigned long long));
-    cudaMemset(trace_dev, 0, TC_TRACE_TILES * 4 * sizeof(unsigned long long));
+    cudaMalloc((void**)&trace_dev, TC_TRACE_WORDS * sizeof(unsigned long long));
+    cudaMemset(trace_dev, 0, TC_TRACE_WORDS * sizeof(unsigned long long));
   }
   do {
     for (int i = 0; i < sets && rc == B2_OK; ++i) {
@@ -1864,7 +1930,7 @@ int b2_gemm_bench(b2_handle* h, int form, int m, int n, int k, int precision, in
     cudaEventElapsedTime(&ms, h->ev_t0, h->ev_t1);
     if (ms_per_iter) *ms_per_iter = (double)ms / iters;
     if (trace_dev) {
-      std::vector<unsigned long long> t(TC_TRACE_TILES * 4);
+      std::vector<unsigned long long> t(TC_TRACE_WORDS);
       cudaMemcpy(t.data(), trace_dev, t.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
       fprintf(stderr, "tile: first MMA -> accumulator complete | complete -> released | released -> last store issued | "
                       "accumulator complete -> next tile's first MMA   (ns, CTA 0)\n");
@@ -1872,6 +1938,14 @@ int b2_gemm_bench(b2_handle* h, int form, int m, int n, int k, int precision, in
         fprintf(stderr, "%3d: %8lld | %8lld | %8lld | %8lld\n", i, (long long)(t[i * 4 + 1] - t[i * 4]),
                 (long long)(t[i * 4 + 2] - t[i * 4 + 1]), (long long)(t[i * 4 + 3] - t[i * 4 + 2]),
                 (i + 1 < TC_TRACE_TILES && t[(i + 1) * 4]) ? (long long)(t[(i + 1) * 4] - t[i * 4 + 1]) : -1LL);
+      const unsigned long long* c = t.data() + TC_TRACE_TILES * 4;
+      fprintf(stderr, "first tile, epilogue warp 0, per chunk (ns): TMEM read + arithmetic, half 0 | half 1 | wait for the "
+                      "buffer | staging + store issue | chunk start relative to the first\n");
+      for (int ch = 0; ch < 8 && c[ch * 8]; ++ch)
+        fprintf(stderr, "  chunk %d: %6lld | %6lld | %6lld | %6lld | %7lld\n", ch, (long long)(c[ch * 8 + 1] - c[ch * 8]),
+                c[ch * 8 + 2] ? (long long)(c[ch * 8 + 2] - c[ch * 8 + 1]) : 0LL,
+                (long long)(c[ch * 8 + 3] - (c[ch * 8 + 2] ? c[ch * 8 + 2] : c[ch * 8 + 1])),
+                (long long)(c[ch * 8 + 4] - c[ch * 8 + 3]), (long long)(c[ch * 8] - c[0]));
     }
     rc = check_status(h);
   } while (0);

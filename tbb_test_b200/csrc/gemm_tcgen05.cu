@@ -435,15 +435,17 @@ __device__ __forceinline__ void epilogue_chunk(const TcParams& p, int row, bool 
 // 32 accumulator columns of one row (this lane's), in place: scale, ReLU (returning the bits
 // of the stored value being positive) or masking by `mask` (bit j = keep column j).
 __device__ __forceinline__ void epilogue_math32(const TcParams& p, uint32_t (&r)[32], uint32_t mask) {
+  // one pass per operation, each a loop of independent elements (the kind of epilogue is uniform)
+  if (p.alpha != 1.f) {
 #pragma unroll
-  for (int j = 0; j < 32; ++j) {
-    float v = __uint_as_float(r[j]) * p.alpha;
-    if (p.epilogue == EPI_RELU) {
-      v = v > 0.f ? v : 0.f;
-    } else if (p.epilogue == EPI_MASK) {
-      v = (mask >> j) & 1u ? v : 0.f;
-    }
-    r[j] = __float_as_uint(v);
+    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * p.alpha);
+  }
+  if (p.epilogue == EPI_RELU) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(fmaxf(__uint_as_float(r[j]), 0.f));
+  } else if (p.epilogue == EPI_MASK) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) r[j] = (mask >> j) & 1u ? r[j] : 0u;
   }
 }
 // mask word of 32 columns from the stored activation itself (callers without a bit plane)
@@ -569,18 +571,29 @@ __device__ __forceinline__ void epilogue_rows_tma(const TcParams& p, const CUten
       uint32_t bits = 0;
       if (p.out_bf16) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const uint32_t w = pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
-          words[half * 16 + j] = w;
-          const uint32_t lo = w & 0xFFFFu, hi = w >> 16;
-          if (lo != 0 && lo < 0x8000u) bits |= 1u << (2 * j);
-          if (hi != 0 && hi < 0x8000u) bits |= 1u << (2 * j + 1);
+        for (int j = 0; j < 16; ++j)
+          words[half * 16 + j] = pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+        if (p.mask_out) {
+          // the plane is written behind a ReLU, so no half is negative: a half is positive iff its low
+          // 15 bits are not all zero; adding 0x7FFF carries into bit 15 (31) exactly then. Four
+          // partial words keep the dependency chains short.
+          uint32_t part[4] = {0, 0, 0, 0};
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const uint32_t m = ((words[half * 16 + j] & 0x7FFF7FFFu) + 0x7FFF7FFFu) & 0x80008000u;
+            part[j & 3] |= (((m >> 15) | (m >> 30)) & 3u) << (2 * j);
+          }
+          bits = (part[0] | part[1]) | (part[2] | part[3]);
         }
       } else {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          words[j] = r[j];
-          if (__uint_as_float(r[j]) > 0.f) bits |= 1u << j;
+        for (int j = 0; j < 32; ++j) words[j] = r[j];
+        if (p.mask_out) {
+          uint32_t part[4] = {0, 0, 0, 0};
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (__uint_as_float(r[j]) > 0.f) part[j & 3] |= 1u << j;
+          bits = (part[0] | part[1]) | (part[2] | part[3]);
         }
       }
       if (p.mask_out && row < p.M && c0 < p.N) p.mask_out[(long long)row * p.ld_mask + (c0 >> 5)] = bits;
@@ -710,6 +723,9 @@ __device__ __forceinline__ void epilogue_bar_sync(int nthreads) {
 
 // ------------------------------------------------------------------------ kernel
 
+// Register budget: the 320 threads of the 256-row mode get 168 registers each (the register file is
+// handed out as if the CTA had 384 threads: 192 per thread was refused at launch), the 192
+// threads of the other modes 255.
 template <int SUB_M>
 __global__ void __launch_bounds__(SUB_M == 2 ? NUM_THREADS_SUB2 : NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,

@@ -48,6 +48,12 @@ struct NcclApi {
   int (*ReduceScatter)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
   int (*AllGather)(const void*, void*, size_t, int, ncclComm_t, cudaStream_t) = nullptr;
   int (*CommGetAsyncError)(ncclComm_t, int*) = nullptr;
+  // optional: buffers allocated by the library and registered with the communicator let its
+  // collectives work on them in place (NVLink SHARP: fewer CTAs, no staging copies)
+  int (*MemAlloc)(void**, size_t) = nullptr;
+  int (*MemFree)(void*) = nullptr;
+  int (*CommRegister)(ncclComm_t, void*, size_t, void**) = nullptr;
+  int (*CommDeregister)(ncclComm_t, void*) = nullptr;
   const char* (*GetErrorString)(int) = nullptr;
   int (*GetVersion)(int*) = nullptr;
   std::string path, error;
@@ -82,6 +88,10 @@ inline NcclApi& nccl_api() {
     api.ReduceScatter = (decltype(api.ReduceScatter))sym("ncclReduceScatter");
     api.AllGather = (decltype(api.AllGather))sym("ncclAllGather");
     api.CommGetAsyncError = (decltype(api.CommGetAsyncError))sym("ncclCommGetAsyncError");
+    api.MemAlloc = (decltype(api.MemAlloc))sym("ncclMemAlloc");
+    api.MemFree = (decltype(api.MemFree))sym("ncclMemFree");
+    api.CommRegister = (decltype(api.CommRegister))sym("ncclCommRegister");
+    api.CommDeregister = (decltype(api.CommDeregister))sym("ncclCommDeregister");
     api.GetErrorString = (decltype(api.GetErrorString))sym("ncclGetErrorString");
     api.GetVersion = (decltype(api.GetVersion))sym("ncclGetVersion");
     api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllReduce && api.ReduceScatter &&

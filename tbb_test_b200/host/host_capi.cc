@@ -105,6 +105,14 @@ void b2h_bucket_slice(const size_t* offset, const size_t* padded, int low, int h
   b2::plan_bucket_slice(offset, padded, low, high, world_size, rank, &out4[0], &out4[1], &out4[2], &out4[3]);
 }
 
+// The rule as the library applies it with the sharded update and the default bucket size: layer 0 in
+// a bucket of its own.
+void b2h_plan_buckets_sharded(const size_t* layer_bytes, int nlayers, int world_size, int ar_bucket_mb, double growth,
+                              int* bucket_low, int* bucket_high) {
+  b2::plan_gradient_buckets(layer_bytes, nlayers, world_size, true, ar_bucket_mb, growth, bucket_low, bucket_high);
+  if (ar_bucket_mb < 0 && world_size > 1) b2::plan_split_lowest_layer(nlayers, bucket_low, bucket_high);
+}
+
 void b2h_ring_info(int nsock, int sid, int task, int* out3) {
   nsockets = nsock;
   get_my_ring_info(sid, task, &out3[0], &out3[1], &out3[2]);

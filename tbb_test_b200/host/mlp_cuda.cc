@@ -8,7 +8,7 @@
 //   mlp_cuda <ngpus> [<nthreads_per_socket, ignored>] [options]
 //     --widths 1024,1024,...   layer widths F_0..F_L     (default: reference model)
 //     --batch N                global batch               (default 1024 * ngpus)
-//     --precision fp32|tf32|bf16                          (default bf16)
+//     --precision fp32|fp32tc|tf32|bf16                   (default bf16)
 //     --mode ref|baseline                                 (default ref, lr 1e-10)
 //     --lr X   --warmup N   --iters N   --no-overlap   --no-allreduce   --graph
 //     --p2p-bytes N            gradient sums up to N bytes through peer memory instead of NCCL
@@ -61,7 +61,7 @@ bool parse(int argc, char** argv, Options* o) {
     } else if (a == "--batch") o->batch = atoi(next());
     else if (a == "--precision") {
       std::string v = next();
-      o->precision = v == "fp32" ? B2_PREC_FP32 : v == "tf32" ? B2_PREC_TF32 : B2_PREC_BF16;
+      o->precision = v == "fp32" ? B2_PREC_FP32 : v == "fp32tc" ? B2_PREC_FP32_TC : v == "tf32" ? B2_PREC_TF32 : B2_PREC_BF16;
     } else if (a == "--mode") {
       std::string v = next();
       o->mode = v == "baseline" ? B2_MODE_BASELINE : B2_MODE_REF;
@@ -152,7 +152,7 @@ int main(int argc, char** argv) {
   Options o;
   if (!parse(argc, argv, &o)) {
     fprintf(stderr,
-            "%s <ngpus> [<nthreads_per_socket>] [--widths a,b,..] [--batch N] [--precision fp32|tf32|bf16]\n"
+            "%s <ngpus> [<nthreads_per_socket>] [--widths a,b,..] [--batch N] [--precision fp32|fp32tc|tf32|bf16]\n"
             "        [--mode ref|baseline] [--lr X] [--warmup N] [--iters N] [--no-overlap] [--no-allreduce] [--graph]\n"
             "        [--p2p-bytes N]\n",
             argv[0]);
