@@ -62,7 +62,8 @@ def main():
 
     # 1b. the same known-answer test and a few steps of the deep narrow shape through the
     # peer-memory path (gradient sums of up to 4 MiB bypass NCCL), against the NCCL path
-    if os.environ.get("B2_TEST_P2P") == "1":
+    # (on two ranks always; on four and eight, where it has not run yet, with B2_TEST_P2P=1)
+    if world == 2 or os.environ.get("B2_TEST_P2P") == "1":
         def connected(dev):
             descs = [None] * world
             dist.all_gather_object(descs, dev.p2p_describe())
