@@ -50,3 +50,31 @@ def test_mlp_cuda_baseline_bf16_runs(native):
     assert r.returncode == 0, r.stdout[-2000:]
     assert re.search(r"samples/s [0-9.e+]+", r.stdout)
     assert "nan" not in r.stdout.lower()
+
+
+def _checksums(args):
+    from tbb_test_b200 import build
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([build.DRIVER] + args, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                       timeout=300, env=env)
+    assert r.returncode == 0, r.stdout[-2000:]
+    sums = re.findall(r"layer (\d+) l1 (\S+) l2 (\S+) trace (\S+)", r.stdout)
+    return np.array([[float(v) for v in s[1:]] for s in sums]), r.stdout
+
+
+@pytest.mark.parametrize("precision,rtol", [("fp32", 5e-5), ("bf16", 2e-3)])
+def test_mlp_cuda_two_gpus_match_one(native, precision, rtol):
+    """The same job on one GPU and split over two (one host thread per GPU, NCCL between them, the
+    reference's allreduce self-check first): the gradient sum over the batch is the same, so the
+    final weights of replica 0 agree up to summation order. The final download is a collective in
+    BF16 precision (the fp32 master weights are gathered from the ranks that own them)."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    common = ["--widths", "384,512,256,128", "--batch", "512", "--warmup", "1", "--iters", "4",
+              "--precision", precision, "--lr", "1e-5"]
+    one, _ = _checksums(["1"] + common)
+    two, out = _checksums(["2"] + common)
+    assert one.shape == two.shape == (3, 3)
+    assert "nan" not in out.lower()
+    assert np.allclose(one, two, rtol=rtol, atol=40 * rtol), (one, two)
