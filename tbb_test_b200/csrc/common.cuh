@@ -49,10 +49,14 @@ struct GemmDesc {
   // Optional in-kernel timeline of the tensor-core kernel (null = off): CTA 0 stamps %globaltimer
   // per tile into trace[tile * 4 + {0: first MMA issued, 1: accumulator complete (seen by the
   // epilogue), 2: accumulator released, 3: last store of the tile issued}], up to TC_TRACE_TILES tiles.
+  // Behind them, for the first TC_TRACE_KBLOCKS k-blocks of CTA 0's second tile: when the MMA warp
+  // saw the k-block's operands in shared memory, when the TMA warp saw the k-block's slot free, and
+  // (CTA-pair kernel) when the peer CTA's TMA warp saw it free.
   unsigned long long* trace;
 };
 constexpr int TC_TRACE_TILES = 64;
-constexpr int TC_TRACE_WORDS = TC_TRACE_TILES * 4 + 64;  // + 8 chunks x 8 stamps of the first tile's epilogue
+constexpr int TC_TRACE_KBLOCKS = 64;
+constexpr int TC_TRACE_WORDS = TC_TRACE_TILES * 4 + 3 * TC_TRACE_KBLOCKS;
 constexpr size_t TC_WS_SLOT_BYTES = 2 * 128 * 256 * sizeof(float);
 
 // CUDA-core GEMM for any shape, stride and alignment (fp32 accumulate).

@@ -1939,13 +1939,14 @@ int b2_gemm_bench(b2_handle* h, int form, int m, int n, int k, int precision, in
                 (long long)(t[i * 4 + 2] - t[i * 4 + 1]), (long long)(t[i * 4 + 3] - t[i * 4 + 2]),
                 (i + 1 < TC_TRACE_TILES && t[(i + 1) * 4]) ? (long long)(t[(i + 1) * 4] - t[i * 4 + 1]) : -1LL);
       const unsigned long long* c = t.data() + TC_TRACE_TILES * 4;
-      fprintf(stderr, "first tile, epilogue warp 0, per chunk (ns): TMEM read + arithmetic, half 0 | half 1 | wait for the "
-                      "buffer | staging + store issue | chunk start relative to the first\n");
-      for (int ch = 0; ch < 8 && c[ch * 8]; ++ch)
-        fprintf(stderr, "  chunk %d: %6lld | %6lld | %6lld | %6lld | %7lld\n", ch, (long long)(c[ch * 8 + 1] - c[ch * 8]),
-                c[ch * 8 + 2] ? (long long)(c[ch * 8 + 2] - c[ch * 8 + 1]) : 0LL,
-                (long long)(c[ch * 8 + 3] - (c[ch * 8 + 2] ? c[ch * 8 + 2] : c[ch * 8 + 1])),
-                (long long)(c[ch * 8 + 4] - c[ch * 8 + 3]), (long long)(c[ch * 8] - c[0]));
+      if (c[0]) {
+        fprintf(stderr, "second tile, per k-block (ns since its first): operands seen by the MMA warp | slot seen free by the "
+                        "TMA warp | by the peer CTA's TMA warp (CTA-pair kernel)\n");
+        for (int kb = 0; kb < TC_TRACE_KBLOCKS && c[kb]; ++kb)
+          fprintf(stderr, "  k-block %2d: %7lld | %7lld | %7lld\n", kb, (long long)(c[kb] - c[0]),
+                  c[TC_TRACE_KBLOCKS + kb] ? (long long)(c[TC_TRACE_KBLOCKS + kb] - c[0]) : 0LL,
+                  c[2 * TC_TRACE_KBLOCKS + kb] ? (long long)(c[2 * TC_TRACE_KBLOCKS + kb] - c[0]) : 0LL);
+      }
     }
     rc = check_status(h);
   } while (0);

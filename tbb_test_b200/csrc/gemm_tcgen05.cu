@@ -56,7 +56,9 @@ constexpr uint32_t X3_CORR_COLS = 256;  // fp32-class mode: TMEM column offset o
 struct TcParams {
   int M, N, K;
   int num_m_blocks, num_n_blocks, num_k_blocks;  // m blocks count super-tiles of sub_m * 128 rows
-  int block_n, block_k;  // block_k in elements (128 bytes of K)
+  int block_n, block_k;  // block_k in elements: 128 bytes of K, or 64 in the half-k-block mode
+  int ksteps;            // MMAs per k-block and 128-row accumulator: block_k bytes / 32
+  uint32_t a_sub_bytes;  // bytes of one 128-row part of the A slab in a stage
   int sub_m;             // 128-row accumulators per tile: 1 (two TMEM stages) or 2 (one stage)
   int acc_stages;
   int num_items;         // work items: whole tiles, then the last partial wave cut in 128-row halves
@@ -275,16 +277,17 @@ __device__ __forceinline__ void mma_issue(uint32_t d, uint64_t adesc, uint64_t b
 template <int SUB_M, bool TF32, bool PAIR>
 __device__ __forceinline__ void issue_kblock(uint32_t tmem_d, uint64_t a_tmpl, uint64_t b_tmpl, uint32_t sa16,
                                              uint32_t sb16, uint32_t a_step16, uint32_t b_step16, uint32_t idesc,
-                                             uint32_t block_n, int sub, bool first_kblock, uint32_t alo16 = 0,
-                                             uint32_t blo16 = 0) {
+                                             uint32_t block_n, int sub, bool first_kblock, int ksteps,
+                                             uint32_t a_sub16, uint32_t alo16 = 0, uint32_t blo16 = 0) {
 #pragma unroll
   for (int ks = 0; ks < KSTEPS; ++ks) {
+    if (ks >= ksteps) break;
     const uint64_t bdesc = b_tmpl + (uint64_t)(sb16 + ks * b_step16);
     const uint32_t accumulate = (ks == 0) ? (first_kblock ? 0u : 1u) : 1u;
 #pragma unroll
     for (int i = 0; i < SUB_M; ++i) {  // the 128-row sub-blocks share the B slab
       if (i < sub) {
-        const uint64_t adesc = a_tmpl + (uint64_t)(sa16 + i * ((BLOCK_M * SLAB_BYTES) >> 4) + ks * a_step16);
+        const uint64_t adesc = a_tmpl + (uint64_t)(sa16 + i * a_sub16 + ks * a_step16);
         const uint32_t d = tmem_d + (uint32_t)i * block_n;
         mma_issue<TF32, PAIR>(d, adesc, bdesc, idesc, accumulate);
         if (TF32 && !PAIR && SUB_M == 1 && alo16 != 0) {
@@ -785,10 +788,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       WorkIter wi;
       Work it;
       work_begin(p, wi);
+      int load_tile = 0;
       while (ok && work_next<SUB_M>(p, wi, it)) {
-        const uint32_t a_bytes = (uint32_t)it.sub * (BLOCK_M * SLAB_BYTES);
+        const uint32_t a_bytes = (uint32_t)it.sub * p.a_sub_bytes;
         for (int kb = it.kb0; kb < it.kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, 1u)) { ok = false; break; }
+          if (p.trace && blockIdx.x == 0 && load_tile == 1 && kb - it.kb0 < TC_TRACE_KBLOCKS)
+            p.trace[TC_TRACE_TILES * 4 + TC_TRACE_KBLOCKS + (kb - it.kb0)] = globaltimer();
           uint8_t* sa = smem + (size_t)stage * stage_bytes;
           uint8_t* sb = sa + p.a_stage_bytes * lo_mul;
           mbar_expect_tx(&full_bar[stage], (a_bytes + p.b_stage_bytes) * lo_mul);
@@ -806,7 +812,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #pragma unroll
               for (int i = 0; i < SUB_M; ++i)
                 if (i < it.sub)
-                  tma_load_2d(ma, &full_bar[stage], da + (size_t)i * (BLOCK_M * SLAB_BYTES), k0, it.m0 + i * BLOCK_M);
+                  tma_load_2d(ma, &full_bar[stage], da + (size_t)i * p.a_sub_bytes, k0, it.m0 + i * BLOCK_M);
             }
             if (p.b_mn) {
               for (int b = 0; b < p.b_boxes; ++b)
@@ -818,6 +824,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           }
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
+        ++load_tile;
       }
       if (!ok) {
         // give copies already in flight a bounded time to land before the CTA retires
@@ -840,6 +847,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       const uint32_t block_n = (uint32_t)p.block_n;
       const bool tf32 = p.kind_tf32 != 0;
       const uint32_t alo16 = p.x3 ? a_stage16 : 0u, blo16 = p.x3 ? (p.b_stage_bytes >> 4) : 0u;
+      const int ksteps = p.ksteps;
+      const uint32_t a_sub16 = p.a_sub_bytes >> 4;
       int trace_tile = 0;
       WorkIter wi;
       Work it;
@@ -851,15 +860,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         for (int kb = it.kb0; kb < it.kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 3u)) { ok = false; break; }
           tc_fence_after();
-          if (p.trace && blockIdx.x == 0 && kb == it.kb0 && trace_tile < TC_TRACE_TILES)
-            p.trace[trace_tile * 4 + 0] = globaltimer();
+          if (p.trace && blockIdx.x == 0) {
+            if (kb == it.kb0 && trace_tile < TC_TRACE_TILES) p.trace[trace_tile * 4 + 0] = globaltimer();
+            if (trace_tile == 1 && kb - it.kb0 < TC_TRACE_KBLOCKS) p.trace[TC_TRACE_TILES * 4 + (kb - it.kb0)] = globaltimer();
+          }
           const uint32_t sa16 = smem16 + (uint32_t)stage * stage16;
           if (tf32)
             issue_kblock<SUB_M, true, false>(tmem_d, a_tmpl, b_tmpl, sa16, sa16 + a_stage16 * lo_mul, a_step16, b_step16,
-                                             idesc, block_n, it.sub, kb == it.kb0, alo16, blo16);
+                                             idesc, block_n, it.sub, kb == it.kb0, ksteps, a_sub16, alo16, blo16);
           else
             issue_kblock<SUB_M, false, false>(tmem_d, a_tmpl, b_tmpl, sa16, sa16 + a_stage16, a_step16, b_step16,
-                                              idesc, block_n, it.sub, kb == it.kb0);
+                                              idesc, block_n, it.sub, kb == it.kb0, ksteps, a_sub16);
           tc_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
@@ -1064,12 +1075,15 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+      int load_tile = 0;
+      for (int t = pair; t < num_tiles && ok; t += num_pairs, ++load_tile) {
         const Item it = decode_item<2>(t, num_tiles, p.num_m_blocks, p.num_n_blocks, p.raster_m, 1 << 30);
         const int m0 = it.m0 + (int)rank * BLOCK_M;                   // this CTA's rows of A
         const int n0 = it.n_blk * p.block_n + (int)rank * (p.block_n / 2);  // this CTA's half of B
         for (int kb = 0; kb < p.num_k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, 1u)) { ok = false; break; }
+          if (p.trace && blockIdx.x < 2 && load_tile == 1 && kb < TC_TRACE_KBLOCKS)  // leader and peer of pair 0
+            p.trace[TC_TRACE_TILES * 4 + (1 + blockIdx.x) * TC_TRACE_KBLOCKS + kb] = globaltimer();
           uint8_t* sa = smem + (size_t)stage * stage_bytes;
           uint8_t* sb = sa + p.a_stage_bytes;
           if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * stage_bytes);  // both CTAs' bytes
@@ -1116,15 +1130,17 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         for (int kb = 0; kb < p.num_k_blocks; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 3u)) { ok = false; break; }
           tc_fence_after();
-          if (p.trace && blockIdx.x == 0 && kb == 0 && trace_tile < TC_TRACE_TILES)
-            p.trace[trace_tile * 4 + 0] = globaltimer();
+          if (p.trace && blockIdx.x == 0) {
+            if (kb == 0 && trace_tile < TC_TRACE_TILES) p.trace[trace_tile * 4 + 0] = globaltimer();
+            if (trace_tile == 1 && kb < TC_TRACE_KBLOCKS) p.trace[TC_TRACE_TILES * 4 + kb] = globaltimer();
+          }
           const uint32_t sa16 = smem16 + (uint32_t)stage * stage16;
           if (tf32)
             issue_kblock<1, true, true>(tmem_d, a_tmpl, b_tmpl, sa16, sa16 + a_stage16, a_step16, b_step16, idesc,
-                                        0u, 1, kb == 0);
+                                        0u, 1, kb == 0, p.ksteps, 0u);
           else
             issue_kblock<1, false, true>(tmem_d, a_tmpl, b_tmpl, sa16, sa16 + a_stage16, a_step16, b_step16, idesc,
-                                         0u, 1, kb == 0);
+                                         0u, 1, kb == 0, p.ksteps, 0u);
           tc_commit_pair(&empty_bar[stage]);
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
@@ -1212,8 +1228,9 @@ EncodeTiledFn get_encode() {
 
 // 2-D tensor map over a row-major matrix: `inner` contiguous elements per row,
 // `outer` rows, `ld` elements between rows; box = box_inner x box_outer.
+// swizzle: 0 = 128 bytes, 1 = 128 bytes in 32-byte atoms, 2 = 64 bytes
 bool make_map(CUtensorMap* map, const void* base, int elem_bytes, long long inner, long long outer, long long ld,
-              int box_inner, int box_outer, bool atom32) {
+              int box_inner, int box_outer, int swizzle) {
   EncodeTiledFn enc = get_encode();
   if (!enc) return false;
   cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
@@ -1222,7 +1239,8 @@ bool make_map(CUtensorMap* map, const void* base, int elem_bytes, long long inne
   cuuint32_t estr[2] = {1, 1};
   CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
   CUresult r = enc(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                   swizzle == 1 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                   : swizzle == 2 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
@@ -1267,7 +1285,6 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
   TcParams& p = plan->p;
   memset(&p, 0, sizeof p);
   p.M = g.M; p.N = g.N; p.K = g.K;
-  p.block_k = SLAB_BYTES / eb;
   // Tile shape: 256 x 256 (two 128-row accumulators sharing each B slab: least shared-memory
   // traffic per flop, but a single accumulator stage), 128 x 256, 128 x 128 or 128 x 64 (two
   // accumulator stages). Chosen by a cost model: waves of the persistent grid times the time
@@ -1318,6 +1335,15 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
     p.pair = (want && !x3 && bn == 256 && (any_count || tiles(2 * BLOCK_M, bn) >= sm_count / 2)) ? 1 : 0;
     if (p.pair) p.sub_m = 2;  // tile rows for the work decomposition: 128 per CTA of the pair
   }
+  // B2_TC_HALF_K=1: k-blocks of 64 bytes of K instead of 128 (64-byte swizzle for K-contiguous
+  // slabs), i.e. a ring with twice the slots of half the size, handed back after half as many
+  // MMAs. Off by default: measured slower (8192 x 4096 x 4096 forward 1023 against 1319 TFLOP/s);
+  // 64-byte rows arrive at 62 GB/s per SM against 93 GB/s for 128-byte rows.
+  bool half_k = false;
+  if (const char* e = getenv("B2_TC_HALF_K")) half_k = e[0] == '1';
+  const int kb_bytes = half_k ? SLAB_BYTES / 2 : SLAB_BYTES;  // bytes of K per k-block
+  p.block_k = kb_bytes / eb;
+  p.ksteps = kb_bytes / KSTEP_BYTES;
   p.acc_stages = (p.sub_m == 2 && !p.pair) ? 1 : 2;
   p.num_m_blocks = (g.M + p.sub_m * BLOCK_M - 1) / (p.sub_m * BLOCK_M);
   p.num_n_blocks = (g.N + bn - 1) / bn;
@@ -1363,8 +1389,14 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
             ((uint32_t)(bn >> 3) << 17) | ((uint32_t)((p.pair ? 2 * BLOCK_M : BLOCK_M) >> 4) << 24);
   const int slab_elems = SLAB_BYTES / eb;
   const int cta_bn = p.pair ? bn / 2 : bn;  // B rows (columns of C) held by one CTA
-  p.a_stage_bytes = (p.pair ? 1 : p.sub_m) * BLOCK_M * SLAB_BYTES;
-  p.b_stage_bytes = cta_bn * SLAB_BYTES;
+  // K-contiguous slabs: rows of kb_bytes, 128-byte swizzle (8-row groups of 1024 B) or, for
+  // half k-blocks, 64-byte swizzle (8-row groups of 512 B, descriptor layout code 4).
+  // M/N-contiguous slabs: boxes of 128 bytes of M or N by block_k k-rows.
+  p.a_sub_bytes = BLOCK_M * kb_bytes;
+  p.a_stage_bytes = (p.pair ? 1 : p.sub_m) * p.a_sub_bytes;
+  p.b_stage_bytes = cta_bn * kb_bytes;
+  const uint32_t k_sbo = 8 * kb_bytes, k_layout = half_k ? 4u : 2u;
+  const int k_swz = half_k ? 2 : 0;  // make_map's swizzle choice
   bool ok = true;
   // M/N-contiguous operands: 16-bit elements use the plain 128-byte swizzle (8 k-rows of
   // 128 B per 1024-byte group); 32-bit elements are only accepted in the variant that
@@ -1381,17 +1413,17 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
     p.a_sbo = mn_group_bytes;
     p.a_layout = mn_layout;
     p.a_kstep = (KSTEP_BYTES / eb) * SLAB_BYTES;
-    ok = ok && make_map(&plan->map_a, g.A, eb, g.M, g.K, lda, slab_elems, p.block_k, mn_atom32);
-    if (x3) ok = ok && make_map(&plan->map_a_lo, g.A_lo, eb, g.M, g.K, lda, slab_elems, p.block_k, mn_atom32);
+    ok = ok && make_map(&plan->map_a, g.A, eb, g.M, g.K, lda, slab_elems, p.block_k, mn_atom32 ? 1 : 0);
+    if (x3) ok = ok && make_map(&plan->map_a_lo, g.A_lo, eb, g.M, g.K, lda, slab_elems, p.block_k, mn_atom32 ? 1 : 0);
   } else {
     p.a_boxes = 1;
-    p.a_box_bytes = BLOCK_M * SLAB_BYTES;
+    p.a_box_bytes = p.a_sub_bytes;
     p.a_lbo = 16;
-    p.a_sbo = 1024;
+    p.a_sbo = k_sbo;
     p.a_kstep = KSTEP_BYTES;
-    p.a_layout = 2;
-    ok = ok && make_map(&plan->map_a, g.A, eb, g.K, g.M, lda, p.block_k, BLOCK_M, false);
-    if (x3) ok = ok && make_map(&plan->map_a_lo, g.A_lo, eb, g.K, g.M, lda, p.block_k, BLOCK_M, false);
+    p.a_layout = k_layout;
+    ok = ok && make_map(&plan->map_a, g.A, eb, g.K, g.M, lda, p.block_k, BLOCK_M, k_swz);
+    if (x3) ok = ok && make_map(&plan->map_a_lo, g.A_lo, eb, g.K, g.M, lda, p.block_k, BLOCK_M, k_swz);
   }
   if (b_mn) {
     p.b_boxes = cta_bn / slab_elems;
@@ -1401,17 +1433,17 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
     p.b_sbo = mn_group_bytes;
     p.b_layout = mn_layout;
     p.b_kstep = (KSTEP_BYTES / eb) * SLAB_BYTES;
-    ok = ok && make_map(&plan->map_b, g.B, eb, g.N, g.K, ldb, slab_elems, p.block_k, mn_atom32);
-    if (x3) ok = ok && make_map(&plan->map_b_lo, g.B_lo, eb, g.N, g.K, ldb, slab_elems, p.block_k, mn_atom32);
+    ok = ok && make_map(&plan->map_b, g.B, eb, g.N, g.K, ldb, slab_elems, p.block_k, mn_atom32 ? 1 : 0);
+    if (x3) ok = ok && make_map(&plan->map_b_lo, g.B_lo, eb, g.N, g.K, ldb, slab_elems, p.block_k, mn_atom32 ? 1 : 0);
   } else {
     p.b_boxes = 1;
     p.b_box_bytes = p.b_stage_bytes;
     p.b_lbo = 16;
-    p.b_sbo = 1024;
+    p.b_sbo = k_sbo;
     p.b_kstep = KSTEP_BYTES;
-    p.b_layout = 2;
-    ok = ok && make_map(&plan->map_b, g.B, eb, g.K, g.N, ldb, p.block_k, cta_bn, false);
-    if (x3) ok = ok && make_map(&plan->map_b_lo, g.B_lo, eb, g.K, g.N, ldb, p.block_k, cta_bn, false);
+    p.b_layout = k_layout;
+    ok = ok && make_map(&plan->map_b, g.B, eb, g.K, g.N, ldb, p.block_k, cta_bn, k_swz);
+    if (x3) ok = ok && make_map(&plan->map_b_lo, g.B_lo, eb, g.K, g.N, ldb, p.block_k, cta_bn, k_swz);
   }
   if (!ok) {
     delete plan;
@@ -1464,6 +1496,10 @@ TcPlan* gemm_tc_plan_create(const GemmDesc& g, int sm_count, char* err, size_t e
   const size_t budget = 227 * 1024 - 1024 /* alignment slack */ - 512 /* static: barriers */;
   int stages = (int)((budget - epi_bytes) / stage);
   if (stages > MAX_STAGES) stages = MAX_STAGES;
+  if (const char* e = getenv("B2_TC_STAGES")) {  // experiments: fewer stages than fit
+    const int want = atoi(e);
+    if (want >= 2 && want < stages) stages = want;
+  }
   if (stages < 2) {
     delete plan;
     return fail("tile does not fit in shared memory");

@@ -155,11 +155,11 @@ def test_unaligned_shape_falls_back_to_cuda_cores(dev, oracle):
         assert rel_fro(c, ref) <= TOL["bf16_f32out"]
 
 
-@pytest.mark.parametrize("variant", ["B2_TC_STREAMK", "B2_TC_PAIR"])
+@pytest.mark.parametrize("variant", ["B2_TC_STREAMK", "B2_TC_PAIR", "B2_TC_HALF_K"])
 def test_optional_tile_schedules(dev, oracle, variant, monkeypatch):
-    """The two opt-in schedules of the tensor-core kernel - stream-K on the tail wave
-    (k-blocks of a tile shared between CTAs through an fp32 workspace) and CTA pairs
-    (cta_group::2) - give the same results as the default one."""
+    """The opt-in schedules of the tensor-core kernel - stream-K on the tail wave (k-blocks of
+    a tile shared between CTAs through an fp32 workspace), CTA pairs (cta_group::2) and
+    half-size k-blocks (64-byte swizzle) - give the same results as the default one."""
     from tbb_test_b200 import _capi as K
     monkeypatch.setenv(variant, "1")
     oracle.use_openblas()
