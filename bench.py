@@ -494,8 +494,11 @@ def main():
     # seeded synthetic data (weights seed 0, inputs seed 1, targets seed 2), drawn in blocks of 256
     # rows from generators keyed by the block number: the global batch is the same whatever the
     # number of ranks, and a rank only draws its own rows
-    x_host = pinned_array((batch, nf[0]))
-    t_host = pinned_array((batch, nf[-1]))
+    # pinned, and on the NUMA node of this rank's GPU (the reference binds each socket's matrices to
+    # its node, mlp_omp.cc:27-47)
+    numa_nodes = []
+    x_host = pinned_array((batch, nf[0]), device=local_rank, node_out=numa_nodes)
+    t_host = pinned_array((batch, nf[-1]), device=local_rank, node_out=numa_nodes)
     for blk in range(b0 // 256, (b1 + 255) // 256):
         r0, r1 = blk * 256, min(batch, blk * 256 + 256)
         xb = np.random.default_rng([1, blk]).standard_normal((r1 - r0, nf[0]), dtype=np.float32)
@@ -669,6 +672,7 @@ def main():
                "h2d_alone_note": "input rows only, pinned memory, every rank copying at the same time "
                                  "(incl. the bf16 conversion kernel): the host link's share of a step is "
                                  "h2d_bytes_per_step / this rate",
+               "host_numa_node_rank0": numa_nodes[0] if numa_nodes else None,
                "call": "b2_train_step_host_async + b2_wait_loss, fp32 host matrices in pinned memory"}
 
     cpu = None

@@ -191,6 +191,15 @@ int b2_wait_loss(b2_handle* h, double* loss);
 int b2_loss(b2_handle* h, double* loss);
 
 int b2_host_alloc(void** ptr, size_t bytes); /* pinned host memory */
+/* Pinned host memory on the NUMA node the GPU `device` hangs off, the counterpart of
+ * create_matrix_with_numa_aware_allocation (mlp_omp.cc:27-47), which binds each socket's
+ * matrices to that socket's node. The node and its CPUs are read from sysfs
+ * (/sys/bus/pci/devices/<bus id>/numa_node, /sys/devices/system/node/node<N>/cpulist); the
+ * calling thread runs on those CPUs while the pages are allocated and touched, then gets its
+ * affinity back. *numa_node (optional) receives the node, or -1 when the system does not tell
+ * (no sysfs entry, a single node, no allowed CPU on that node): the call then behaves like
+ * b2_host_alloc. Freed by b2_host_free. */
+int b2_host_alloc_near(void** ptr, size_t bytes, int device, int* numa_node);
 int b2_host_free(void* ptr);
 
 /* The three cblas_sgemm call sites (mlp_omp.cc:474,566,657) with cblas argument

@@ -60,6 +60,7 @@ SYMBOLS = {
     "b2_wait_loss": (C.c_int, [_H, _dp]),
     "b2_loss": (C.c_int, [_H, _dp]),
     "b2_host_alloc": (C.c_int, [C.POINTER(C.c_void_p), C.c_size_t]),
+    "b2_host_alloc_near": (C.c_int, [C.POINTER(C.c_void_p), C.c_size_t, C.c_int, C.POINTER(C.c_int)]),
     "b2_host_free": (C.c_int, [C.c_void_p]),
     "b2_sgemm_host": (C.c_int, [_H, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _fp, C.c_size_t, _fp,
                                 C.c_size_t, _fp, C.c_size_t, C.c_int, _fp, C.c_size_t]),

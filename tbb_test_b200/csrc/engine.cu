@@ -14,9 +14,11 @@
 // by dedicating threads: mlp_omp.cc:520-527,601-615,692-723).
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <sched.h>
 #include <unistd.h>
 
 #include <algorithm>
+#include <cctype>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -1463,6 +1465,56 @@ int b2_host_alloc(void** ptr, size_t bytes) {
   if (!ptr) return B2_ERR_INVALID;
   cudaError_t e = cudaHostAlloc(ptr, bytes, cudaHostAllocDefault);
   if (e != cudaSuccess) return fail(nullptr, B2_ERR_CUDA, "cudaHostAlloc: %s", cudaGetErrorString(e));
+  return B2_OK;
+}
+
+int b2_host_alloc_near(void** ptr, size_t bytes, int device, int* numa_node) {
+  if (!ptr) return B2_ERR_INVALID;
+  if (numa_node) *numa_node = -1;
+  cpu_set_t old_set, node_set;
+  bool bound = false;
+  int node = -1;
+  char bus[32] = "";
+  if (cudaDeviceGetPCIBusId(bus, sizeof bus, device) == cudaSuccess &&
+      sched_getaffinity(0, sizeof old_set, &old_set) == 0) {
+    for (char* c = bus; *c; ++c) *c = (char)tolower((unsigned char)*c);
+    char path[128];
+    snprintf(path, sizeof path, "/sys/bus/pci/devices/%s/numa_node", bus);
+    if (FILE* f = fopen(path, "r")) {
+      if (fscanf(f, "%d", &node) != 1) node = -1;
+      fclose(f);
+    }
+    if (node >= 0) {
+      // "0-31,64-95": the CPUs of the node, kept only where this thread may already run
+      CPU_ZERO(&node_set);
+      int kept = 0;
+      snprintf(path, sizeof path, "/sys/devices/system/node/node%d/cpulist", node);
+      if (FILE* f = fopen(path, "r")) {
+        int lo, hi;
+        while (fscanf(f, "%d", &lo) == 1) {
+          hi = lo;
+          int ch = fgetc(f);
+          if (ch == '-') {
+            if (fscanf(f, "%d", &hi) != 1) break;
+            ch = fgetc(f);
+          }
+          for (int c = lo; c <= hi && c < CPU_SETSIZE; ++c)
+            if (c >= 0 && CPU_ISSET(c, &old_set)) {
+              CPU_SET(c, &node_set);
+              ++kept;
+            }
+          if (ch != ',') break;
+        }
+        fclose(f);
+      }
+      if (kept > 0 && sched_setaffinity(0, sizeof node_set, &node_set) == 0) bound = true;
+    }
+  }
+  cudaError_t e = cudaHostAlloc(ptr, bytes, cudaHostAllocDefault);
+  if (e == cudaSuccess && bound) memset(*ptr, 0, bytes);  // touched from the node's CPUs
+  if (bound) sched_setaffinity(0, sizeof old_set, &old_set);
+  if (e != cudaSuccess) return fail(nullptr, B2_ERR_CUDA, "cudaHostAlloc: %s", cudaGetErrorString(e));
+  if (numa_node && bound) *numa_node = node;
   return B2_OK;
 }
 

@@ -280,12 +280,20 @@ class MLP:
         self._ck(self.lib.b2_sync(self._h))
 
 
-def pinned_array(shape):
+def pinned_array(shape, device=None, node_out=None):
     """A float32 numpy array over pinned host memory from b2_host_alloc (never freed
-    explicitly: it lives as long as the process, which is how the benchmark uses it)."""
+    explicitly: it lives as long as the process, which is how the benchmark uses it).
+    With `device`, the pages come from the NUMA node of that GPU (b2_host_alloc_near);
+    `node_out`, a list, then receives the node (-1: the system does not tell)."""
     n = int(np.prod(shape))
     p = C.c_void_p()
-    rc = K.lib().b2_host_alloc(C.byref(p), n * 4)
+    if device is None:
+        rc = K.lib().b2_host_alloc(C.byref(p), n * 4)
+    else:
+        node = C.c_int(-1)
+        rc = K.lib().b2_host_alloc_near(C.byref(p), n * 4, int(device), C.byref(node))
+        if node_out is not None:
+            node_out.append(node.value)
     if rc != K.OK:
         raise K.B2Error(rc, K.lib().b2_last_error(None).decode())
     buf = (C.c_float * n).from_address(p.value)

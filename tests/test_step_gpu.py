@@ -417,3 +417,32 @@ def test_measurement_entry_points(native, oracle):
     host = np.zeros(16, np.float32)
     assert dev.lib.b2_allreduce(dev._h, host.ctypes.data, 16, K.DTYPE_F32) == K.ERR_INVALID
     dev.close()
+
+
+def test_pinned_memory_near_the_gpu(native):
+    """b2_host_alloc_near: pinned pages from the NUMA node of the GPU (the reference's
+    create_matrix_with_numa_aware_allocation, mlp_omp.cc:27-47). The node is whatever sysfs says
+    (-1 where it says nothing); the memory is usable, the thread's CPU affinity is as before, and
+    a host-fed step from it gives the same loss as one fed from plain pinned memory."""
+    import os
+    from tbb_test_b200 import _capi as K
+    from tbb_test_b200.mlp import MLP, pinned_array
+    before = os.sched_getaffinity(0)
+    nodes = []
+    x = pinned_array((256, 128), device=0, node_out=nodes)
+    t = pinned_array((256, 64), device=0, node_out=nodes)
+    assert os.sched_getaffinity(0) == before
+    assert len(nodes) == 2 and nodes[0] == nodes[1] and nodes[0] >= -1
+    rng = np.random.default_rng(5)
+    x[:] = rng.standard_normal(x.shape, dtype=np.float32)
+    t[:] = np.sign(rng.standard_normal(t.shape)).astype(np.float32)
+    x2, t2 = pinned_array(x.shape), pinned_array(t.shape)
+    x2[:], t2[:] = x, t
+    losses = []
+    for xs, ts in ((x, t), (x2, t2)):
+        dev = MLP([128, 96, 64], 256, precision=K.PREC_BF16, mode=K.MODE_BASELINE, lr=0.01)
+        for l, (fo, fi) in enumerate([(96, 128), (64, 96)]):
+            dev.upload_weights(l, np.random.default_rng(l).uniform(-0.1, 0.1, (fo, fi)).astype(np.float32))
+        losses.append(dev.train_step_host(xs.ctypes.data_as(K._fp), 128, ts.ctypes.data_as(K._fp), 64))
+        dev.close()
+    assert losses[0] == losses[1] and np.isfinite(losses[0])
