@@ -271,17 +271,24 @@ int check_comm(b2_handle* h) {
   return B2_OK;
 }
 
+// Rows of `width` bytes between two pitched buffers: one flat copy when both are dense.
+cudaError_t copy_rows(void* dst, size_t dpitch, const void* src, size_t spitch, size_t width, size_t rows,
+                      cudaMemcpyKind kind, cudaStream_t st) {
+  if (dpitch == width && spitch == width) return cudaMemcpyAsync(dst, src, width * rows, kind, st);
+  return cudaMemcpy2DAsync(dst, dpitch, src, spitch, width, rows, kind, st);
+}
+
 // Host (ld) <-> dense device matrix of `type`, through the fp32 staging buffer when
 // the device holds bf16.
 int upload_matrix(b2_handle* h, void* dev, int type, const float* host, size_t ld, int rows, int cols) {
   if (rows <= 0 || cols <= 0) return B2_OK;
   if (type == T_F32) {
-    CK(h, cudaMemcpy2DAsync(dev, (size_t)cols * 4, host, ld * 4, (size_t)cols * 4, rows, cudaMemcpyHostToDevice,
-                            h->s_main));
+    CK(h, copy_rows(dev, (size_t)cols * 4, host, ld * 4, (size_t)cols * 4, (size_t)rows, cudaMemcpyHostToDevice,
+                    h->s_main));
   } else {
     if ((size_t)rows * cols > h->stage_elems) return fail(h, B2_ERR_INVALID, "staging buffer too small");
-    CK(h, cudaMemcpy2DAsync(h->stage, (size_t)cols * 4, host, ld * 4, (size_t)cols * 4, rows,
-                            cudaMemcpyHostToDevice, h->s_main));
+    CK(h, copy_rows(h->stage, (size_t)cols * 4, host, ld * 4, (size_t)cols * 4, (size_t)rows,
+                    cudaMemcpyHostToDevice, h->s_main));
     CK(h, convert_f32_to_bf16(h->stage, (__nv_bfloat16*)dev, (size_t)rows * cols, h->s_main));
     ++h->launches;
   }
@@ -1417,8 +1424,8 @@ int b2_train_step_host_async(b2_handle* h, const float* x, size_t ldx, const flo
   if (rows > 0) {
     void* act0 = slot ? h->act0_alt : h->act[0];
     void* land = h->op_type == T_BF16 ? (void*)h->xstage[slot] : act0;
-    CK(h, cudaMemcpy2DAsync(land, (size_t)f0 * 4, x + (size_t)h->b0 * ldx, ldx * 4, (size_t)f0 * 4, rows,
-                            cudaMemcpyHostToDevice, h->s_copy));
+    CK(h, copy_rows(land, (size_t)f0 * 4, x + (size_t)h->b0 * ldx, ldx * 4, (size_t)f0 * 4, (size_t)rows,
+                    cudaMemcpyHostToDevice, h->s_copy));
     if (h->op_type == T_BF16) {
       CK(h, convert_f32_to_bf16(h->xstage[slot], (__nv_bfloat16*)act0, (size_t)rows * f0, h->s_copy));
       ++h->launches;
@@ -1429,8 +1436,8 @@ int b2_train_step_host_async(b2_handle* h, const float* x, size_t ldx, const flo
       ++h->launches;
     }
     if (t)
-      CK(h, cudaMemcpy2DAsync(slot ? h->target_alt : h->target, (size_t)fl * 4, t + (size_t)h->b0 * ldt, ldt * 4,
-                              (size_t)fl * 4, rows, cudaMemcpyHostToDevice, h->s_copy));
+      CK(h, copy_rows(slot ? h->target_alt : h->target, (size_t)fl * 4, t + (size_t)h->b0 * ldt, ldt * 4,
+                      (size_t)fl * 4, (size_t)rows, cudaMemcpyHostToDevice, h->s_copy));
   }
   CK(h, cudaEventRecord(h->ev_copied[slot], h->s_copy));
   CK(h, cudaStreamWaitEvent(h->s_main, h->ev_copied[slot], 0));
