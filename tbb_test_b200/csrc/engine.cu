@@ -80,6 +80,7 @@ struct b2_handle {
   bool nccl_ub = false;
   void* ub_handle[3] = {nullptr, nullptr, nullptr};
   bool ag_deferred = true;     // allgathers behind all reduce-scatters of a step, lowest bucket first
+  bool ag_grouped = false;     // B2_AG_ORDER=grouped: each allgather in one NCCL group with the next reduce-scatter
   bool shard = false;          // reduce-scatter + owned-slice SGD + allgather instead of allreduce + full SGD
   bool masters_stale = false;  // BF16 precision with shard: ranks hold current fp32 masters only for their slices
   std::vector<size_t> dw_pad;  // padded element count of layer l in the slabs (multiple of 128 * world)
@@ -521,6 +522,39 @@ int bucket_allgather(b2_handle* h, int low, int high, cudaStream_t st, bool time
 }
 
 // Whether the bucket closed by layer `low` takes the sharded route (else: full sum + full SGD).
+// Reduce-scatter of bucket [low, high] and allgather of bucket [ag_low, ag_high] (updated before)
+// in one NCCL group: one launch in which the two run side by side on separate channels.
+int bucket_rs_ag_grouped(b2_handle* h, int low, int high, int ag_low, int ag_high, cudaStream_t st, bool timed) {
+  size_t rb, rc_, ab, ac;
+  bucket_range(h, low, high, &rb, &rc_);
+  bucket_range(h, ag_low, ag_high, &ab, &ac);
+  const int world = h->cfg.world_size, rank = h->cfg.rank;
+  const size_t es = esize(h->grad_type), rper = rc_ / world, aper = ac / world;
+  char* gbase = static_cast<char*>(h->dw_slab) + rb * es;
+  if (timed) CK(h, cudaEventRecord(phase_ev(h, low, B2_T_ALLREDUCE, 0), st));
+  NCK(h, nccl_api().GroupStart());
+  NCK(h, nccl_api().ReduceScatter(gbase, gbase + (size_t)rank * rper * es, rper,
+                                  h->grad_type == T_BF16 ? ncclBfloat16 : ncclFloat32, ncclSum, h->comm, st));
+  if (h->op_type == T_BF16) {
+    __nv_bfloat16* base = h->w16_slab + ab;
+    NCK(h, nccl_api().AllGather(base + (size_t)rank * aper, base, aper, ncclBfloat16, h->comm, st));
+  } else {
+    float* base = h->w_slab + ab;
+    NCK(h, nccl_api().AllGather(base + (size_t)rank * aper, base, aper, ncclFloat32, h->comm, st));
+  }
+  NCK(h, nccl_api().GroupEnd());
+  if (h->op_type != T_BF16 && h->x3) {
+    CK(h, split_lo_launch(h->w_slab + ab, h->w_lo_slab + ab, ac, st));
+    ++h->launches;
+  }
+  if (timed) {  // the pair counts as the reduce-scatter's phase; the allgather's own phase is empty
+    CK(h, cudaEventRecord(phase_ev(h, low, B2_T_ALLREDUCE, 1), st));
+    CK(h, cudaEventRecord(phase_ev(h, ag_low, B2_T_ALLGATHER, 0), st));
+    CK(h, cudaEventRecord(phase_ev(h, ag_low, B2_T_ALLGATHER, 1), st));
+  }
+  return B2_OK;
+}
+
 bool bucket_sharded(const b2_handle* h, int low) {
   return h->shard && !h->bucket_full[low];
 }
@@ -615,7 +649,20 @@ int enqueue_step(b2_handle* h, bool timed, int slot = 0) {
     if (sharded) {
       // reduce-scatter of this bucket; behind it, on the same stream, the allgather of the bucket
       // before (its owned-slice SGD ran while this reduce-scatter was in flight)
-      if ((rc = bucket_reduce_scatter(h, l, h->bucket_high[l], sc, timed))) return rc;
+      if (h->ag_grouped && pending_ag >= 0) {
+        if (overlap) CK(h, cudaStreamWaitEvent(sc, h->ev_shard[pending_ag], 0));
+        if ((rc = bucket_rs_ag_grouped(h, l, h->bucket_high[l], pending_ag, h->bucket_high[pending_ag], sc, timed)))
+          return rc;
+        for (int k = pending_ag; k <= h->bucket_high[pending_ag]; ++k) {
+          if (overlap) {
+            CK(h, cudaEventRecord(h->ev_upd[k], sc));
+            h->upd_pending[k] = 1;
+          }
+        }
+        pending_ag = -1;
+      } else if ((rc = bucket_reduce_scatter(h, l, h->bucket_high[l], sc, timed))) {
+        return rc;
+      }
       if (overlap) CK(h, cudaEventRecord(h->ev_ar[l], sc));
       if (pending_ag >= 0 && ag_deferred && ndeferred < 64) {
         deferred[ndeferred++] = pending_ag;
@@ -1000,7 +1047,8 @@ int b2_create(const b2_config* cfg, b2_handle** out) {
                           h->bucket_low.data(), h->bucket_high.data());
     {
       const char* e = getenv("B2_AG_ORDER");
-      h->ag_deferred = !(e && e[0] == 'e');
+      h->ag_deferred = !(e && (e[0] == 'e' || e[0] == 'g'));
+      h->ag_grouped = e && e[0] == 'g' && nccl_api().GroupStart && nccl_api().GroupEnd;
       // layer 0 in a bucket of its own (bucket_plan.h) unless the bucket size was given explicitly
       // (ar_bucket_mb >= 0) or B2_SPLIT_LAST=0
       const char* sl = getenv("B2_SPLIT_LAST");

@@ -47,6 +47,8 @@ struct NcclApi {
   int (*AllReduce)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
   int (*ReduceScatter)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
   int (*AllGather)(const void*, void*, size_t, int, ncclComm_t, cudaStream_t) = nullptr;
+  int (*GroupStart)() = nullptr;  // optional
+  int (*GroupEnd)() = nullptr;
   int (*CommGetAsyncError)(ncclComm_t, int*) = nullptr;
   // optional: buffers allocated by the library and registered with the communicator let its
   // collectives work on them in place (NVLink SHARP: fewer CTAs, no staging copies)
@@ -87,6 +89,8 @@ inline NcclApi& nccl_api() {
     api.AllReduce = (decltype(api.AllReduce))sym("ncclAllReduce");
     api.ReduceScatter = (decltype(api.ReduceScatter))sym("ncclReduceScatter");
     api.AllGather = (decltype(api.AllGather))sym("ncclAllGather");
+    api.GroupStart = (decltype(api.GroupStart))sym("ncclGroupStart");
+    api.GroupEnd = (decltype(api.GroupEnd))sym("ncclGroupEnd");
     api.CommGetAsyncError = (decltype(api.CommGetAsyncError))sym("ncclCommGetAsyncError");
     api.MemAlloc = (decltype(api.MemAlloc))sym("ncclMemAlloc");
     api.MemFree = (decltype(api.MemFree))sym("ncclMemFree");

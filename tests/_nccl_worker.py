@@ -109,7 +109,14 @@ def main():
                                 (K.PREC_BF16, O.ROUND_BF16, dict(state=5e-3, grad=1e-1))):
         # two-stream schedule with the default gradient buckets, with one collective per layer,
         # and the serial schedule; sharded update (default) and allreduce + full update
-        for overlap, bucket, shard in ((True, -1, 1), (True, 0, 1), (False, -1, 1), (True, -1, 0), (False, 0, 0)):
+        # ... and, one bucket per layer, the two other allgather orders of the sharded update
+        for overlap, bucket, shard, ag_order in ((True, -1, 1, None), (True, 0, 1, None), (False, -1, 1, None),
+                                                 (True, -1, 0, None), (False, 0, 0, None),
+                                                 (True, 0, 1, "eager"), (True, 0, 1, "grouped")):
+            if ag_order:
+                os.environ["B2_AG_ORDER"] = ag_order
+            else:
+                os.environ.pop("B2_AG_ORDER", None)
             dev = MLP(nf, batch, rank=rank, world_size=world, device=local, precision=prec, lr=0.01,
                       nccl_id=fresh_id(), overlap=overlap, ar_bucket_mb=bucket, shard_update=shard)
             orc = O.Oracle(nf, batch, nranks=world, mode=O.MODE_BASELINE, rounding=rounding, lr=0.01)
@@ -134,6 +141,7 @@ def main():
             assert abs(loss.item() - orc.loss()) <= 2e-3 * abs(orc.loss())
             dev.close()
             orc.close()
+    os.environ.pop("B2_AG_ORDER", None)
     dist.barrier()
     dist.destroy_process_group()
     print(f"rank {rank}: ok")
